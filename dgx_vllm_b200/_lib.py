@@ -1,0 +1,67 @@
+"""ctypes binding of libb200nvfp4.so (the C ABI declared in include/b200_nvfp4.h).
+
+There is no CPU or PyTorch fallback: if the library is missing or an entry point returns a
+non-zero status the call raises."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libb200nvfp4.so")
+
+F16, BF16, F32 = 0, 1, 2
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_i32 = ctypes.c_int
+_sz = ctypes.c_size_t
+
+# name -> (restype, argtypes); must list every symbol include/b200_nvfp4.h declares
+SIGNATURES = {
+    "b200fp4_get_error_string": (ctypes.c_char_p, [_i32]),
+    "b200fp4_version": (_i32, []),
+    "b200fp4_version_string": (ctypes.c_char_p, []),
+    "b200fp4_has_hardware_acceleration": (_i32, []),
+    "b200fp4_launch_count": (ctypes.c_uint64, []),
+    "b200fp4_sf_swizzled_bytes": (_sz, [_i64, _i64]),
+    "b200fp4_quantize": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
+    "b200fp4_experts_quantize": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "b200fp4_sparse_workspace_bytes": (_sz, [_i64, _i64]),
+    "b200fp4_sparse_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_dense_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_sparse_packed_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_fused_moe_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
+                                        _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+}
+
+_lib = None
+
+
+class B200Fp4Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().b200fp4_get_error_string(status).decode()
+        super().__init__(f"{where}: status {status} ({msg})")
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m dgx_vllm_b200.build` (needs nvcc). "
+                "This package has no fallback path.")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != 0:
+        raise B200Fp4Error(status, where)

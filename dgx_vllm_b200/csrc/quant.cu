@@ -1,0 +1,191 @@
+// bf16/f16 -> NVFP4 quantizer for sm_100a.
+//
+// One thread owns 8 consecutive elements (one 16-byte load); two neighbouring lanes form one
+// 16-element scale block and share the block maximum through a warp shuffle.  Codes leave as one
+// 4-byte store per thread, so a warp reads 512 contiguous bytes per row segment and writes 128.
+// Arithmetic follows ref_nvfp4_quant (vllm/model_executor/layers/quantization/utils/
+// nvfp4_emulation_utils.py:439-453) operation by operation in IEEE fp32 -- explicit _rn
+// intrinsics keep the compiler from contracting or approximating -- so codes and scales are
+// bit-identical to the reference's emulation path; the E2M1 rounding itself is the native
+// cvt.rn.satfinite.e2m1x2.f32 that replaces the reference's software routine
+// (patch_nvfp4_utils_sw_e2m1.py:31-63).
+#include "common.cuh"
+
+namespace b200fp4 {
+
+std::atomic<uint64_t> g_launch_count{0};
+
+namespace {
+
+constexpr int kTX = 64;    // threads along K (each 8 elements): 512 elements per block row
+constexpr int kTY = 4;     // rows per block per pass
+constexpr int kRows = 4;   // passes (rows) per thread, loads issued together
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float* v) {
+  const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(h[i]);
+}
+
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+
+// kExperts: per-row expert lookup (global scale + scale-factor row offset per expert).
+// kSilu:    input is [M, 2K]; quantize round_to_T(silu(x[:, :K]) * x[:, K:]).
+template <typename T, bool kSwizzled, bool kExperts, bool kSilu>
+__global__ void __launch_bounds__(kTX* kTY)
+    quantize_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const float* __restrict__ gs_ptr,
+                    const int32_t* __restrict__ expert_offsets, const int32_t* __restrict__ blockscale_offsets,
+                    int num_experts, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+  const int64_t kc = (int64_t)blockIdx.x * kTX + threadIdx.x;  // 8-element chunk index along K
+  const int64_t CPR = K >> 3;
+  const int64_t KB = K >> 4;
+  const int64_t KT = (KB + 3) >> 2;
+  const int64_t m0 = ((int64_t)blockIdx.y * kTY + threadIdx.y) * kRows;
+  const bool col_ok = kc < CPR;
+
+  uint4 raw[kRows], raw2[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    raw[r] = make_uint4(0, 0, 0, 0);
+    raw2[r] = make_uint4(0, 0, 0, 0);
+    const int64_t m = m0 + r;
+    if (col_ok && m < M) {
+      raw[r] = *reinterpret_cast<const uint4*>(x + m * ldx + kc * 8);
+      if (kSilu) raw2[r] = *reinterpret_cast<const uint4*>(x + m * ldx + K + kc * 8);
+    }
+  }
+
+  float gs_shared = 0.f;
+  if (!kExperts) gs_shared = gs_ptr[0];
+
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int64_t m = m0 + r;
+    const bool ok = col_ok && m < M;
+    float v[8];
+    unpack8<T>(raw[r], v);
+    if (kSilu) {
+      float u[8];
+      unpack8<T>(raw2[r], u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(from_f32<T>(silu_f32(v[i]) * u[i]));
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+
+    float gs = gs_shared;
+    int64_t sf_row = m;
+    if (kExperts) {
+      // largest e with expert_offsets[e] <= m
+      int lo = 0, hi = num_experts - 1;
+      if (ok) {
+        while (lo < hi) {
+          int mid = (lo + hi + 1) >> 1;
+          if ((int64_t)expert_offsets[mid] <= m) lo = mid;
+          else hi = mid - 1;
+        }
+        gs = gs_ptr[lo];
+        sf_row = (int64_t)blockscale_offsets[lo] + (m - (int64_t)expert_offsets[lo]);
+      }
+    }
+
+    const float rcp_gs = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
+    float scale = __fmul_rn(gs, __fmul_rn(amax, 0.16666667163372039794921875f));  // fl32(1/6)
+    scale = fminf(scale, 448.f);
+    const uint8_t sfb = f32_to_e4m3(scale);
+    const float t = __fmul_rn(e4m3_to_f32(sfb), rcp_gs);
+    const float os = __frcp_rn(t + (t == 0.f ? 1.0e8f : 0.f));
+
+    const uint32_t packed =
+        f32x8_to_e2m1(__fmul_rn(v[0], os), __fmul_rn(v[1], os), __fmul_rn(v[2], os), __fmul_rn(v[3], os),
+                      __fmul_rn(v[4], os), __fmul_rn(v[5], os), __fmul_rn(v[6], os), __fmul_rn(v[7], os));
+    if (ok) {
+      *reinterpret_cast<uint32_t*>(codes + m * (K >> 1) + kc * 4) = packed;
+      if ((kc & 1) == 0) {
+        const int64_t kb = kc >> 1;
+        if (kSwizzled) sf[sf_swizzled_offset(sf_row, kb, KT)] = sfb;
+        else sf[sf_row * KB + kb] = sfb;
+      }
+    }
+  }
+}
+
+template <typename T, bool kSwz, bool kExp, bool kSilu>
+void launch(const void* x, int64_t M, int64_t K, int64_t ldx, const float* gs, const int32_t* eo, const int32_t* bo,
+            int ne, void* codes, void* sf, cudaStream_t st) {
+  dim3 block(kTX, kTY);
+  dim3 grid((unsigned)(((K >> 3) + kTX - 1) / kTX), (unsigned)((M + kTY * kRows - 1) / (kTY * kRows)));
+  quantize_kernel<T, kSwz, kExp, kSilu><<<grid, block, 0, st>>>(reinterpret_cast<const T*>(x), M, K, ldx, gs, eo, bo,
+                                                                ne, (uint8_t*)codes, (uint8_t*)sf);
+}
+
+}  // namespace
+}  // namespace b200fp4
+
+using namespace b200fp4;
+
+extern "C" size_t b200fp4_sf_swizzled_bytes(int64_t rows, int64_t k_blocks) {
+  if (rows < 0 || k_blocks < 0) return 0;
+  return (size_t)(((rows + 127) / 128) * 128 * (((k_blocks + 3) / 4) * 4));
+}
+
+extern "C" int b200fp4_quantize(const void* x, int in_dtype, int64_t M, int64_t K, int64_t ldx,
+                                const float* global_scale, void* codes, void* sf, int sf_swizzled, void* stream) {
+  if (M < 0 || K <= 0 || (K % 16) != 0 || ldx < K || (ldx % 8) != 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (in_dtype != B200FP4_DTYPE_F16 && in_dtype != B200FP4_DTYPE_BF16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (M == 0) return B200FP4_STATUS_SUCCESS;
+  if (!x || !global_scale || !codes || !sf) return B200FP4_STATUS_INVALID_VALUE;
+  if (!aligned(x, 16) || !aligned(codes, 4)) return B200FP4_STATUS_INVALID_VALUE;
+  if (M > (int64_t)65535 * kTY * kRows) return B200FP4_STATUS_NOT_SUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  int n_launch = 1;
+  const int64_t KB = K / 16;
+  if (sf_swizzled && ((M % 128) != 0 || (KB % 4) != 0)) {
+    if (cudaMemsetAsync(sf, 0, b200fp4_sf_swizzled_bytes(M, KB), st) != cudaSuccess) {
+      cudaGetLastError();
+      return B200FP4_STATUS_EXECUTION_FAILED;
+    }
+    ++n_launch;
+  }
+  const bool bf = in_dtype == B200FP4_DTYPE_BF16;
+  if (sf_swizzled) {
+    if (bf) launch<__nv_bfloat16, true, false, false>(x, M, K, ldx, global_scale, nullptr, nullptr, 0, codes, sf, st);
+    else launch<__half, true, false, false>(x, M, K, ldx, global_scale, nullptr, nullptr, 0, codes, sf, st);
+  } else {
+    if (bf) launch<__nv_bfloat16, false, false, false>(x, M, K, ldx, global_scale, nullptr, nullptr, 0, codes, sf, st);
+    else launch<__half, false, false, false>(x, M, K, ldx, global_scale, nullptr, nullptr, 0, codes, sf, st);
+  }
+  return finish_launch(n_launch);
+}
+
+extern "C" int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,
+                                        const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                        int32_t num_experts, int64_t sf_rows_padded, int silu_mul, void* codes,
+                                        void* sf, void* stream) {
+  if (M < 0 || K <= 0 || (K % 16) != 0 || num_experts <= 0 || sf_rows_padded < 0 || (sf_rows_padded % 128) != 0)
+    return B200FP4_STATUS_INVALID_VALUE;
+  if (in_dtype != B200FP4_DTYPE_F16 && in_dtype != B200FP4_DTYPE_BF16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (!global_scales || !expert_offsets || !blockscale_offsets || !sf) return B200FP4_STATUS_INVALID_VALUE;
+  if (M > 0 && (!x || !codes || !aligned(x, 16) || !aligned(codes, 4))) return B200FP4_STATUS_INVALID_VALUE;
+  if (M > (int64_t)65535 * kTY * kRows) return B200FP4_STATUS_NOT_SUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t KB = K / 16;
+  if (cudaMemsetAsync(sf, 0, (size_t)(sf_rows_padded * (((KB + 3) / 4) * 4)), st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  if (M == 0) return finish_launch(1);
+  const bool bf = in_dtype == B200FP4_DTYPE_BF16;
+  const int64_t ldx = silu_mul ? 2 * K : K;
+  if (silu_mul) {
+    if (bf) launch<__nv_bfloat16, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+    else launch<__half, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+  } else {
+    if (bf) launch<__nv_bfloat16, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+    else launch<__half, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+  }
+  return finish_launch(2);
+}

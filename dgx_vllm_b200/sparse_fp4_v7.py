@@ -1,0 +1,171 @@
+"""Drop-in mirror of the reference's `sparse_fp4_v7` extension module.
+
+Same function names, positional order and tensor formats as the pybind module defined at
+sparse_fp4_kernel/sparse_fp4_v7.cu:744-749 of Avarok-Cybersecurity/dgx-vllm, backed by the
+sm_100a kernels in libb200nvfp4.so.  Differences a caller can observe:
+  * arguments are validated (device, dtype, shape, contiguity) and a RuntimeError is raised on
+    misuse, where the reference has undefined behaviour;
+  * bf16 activations are taken natively and the result comes back in the activation dtype
+    (the reference casts bf16 to fp16 first and always returns fp16); pass out_dtype to force one;
+  * expert ids outside [0, E) -- e.g. -1 from an expert-parallel expert_map -- give a zero
+    contribution instead of an out-of-bounds read;
+  * the sign bit of a block scale is ignored (block scales are magnitudes).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._torch_util import dtype_code, ptr, require, require_cuda, stream_ptr, workspace
+
+
+def _check_act(A: torch.Tensor, name: str) -> None:
+    require(A.dim() == 2, f"{name} must be 2-D")
+    require(A.dtype in (torch.float16, torch.bfloat16), f"{name} must be float16 or bfloat16")
+    require(A.is_contiguous(), f"{name} must be contiguous")
+
+
+def _check_u8(t: torch.Tensor, name: str, ndim: int = 3) -> None:
+    require(t.dim() == ndim, f"{name} must be {ndim}-D")
+    require(t.dtype in (torch.uint8, torch.float8_e4m3fn), f"{name} must be uint8")
+    require(t.is_contiguous(), f"{name} must be contiguous")
+
+
+def _ids_i32(ids: torch.Tensor) -> torch.Tensor:
+    ids = ids.reshape(-1)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    return ids.contiguous()
+
+
+def _out_dtype(A: torch.Tensor, out_dtype) -> torch.dtype:
+    return A.dtype if out_dtype is None else out_dtype
+
+
+def batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, *, out_dtype=None):
+    """out[p] = A[p] . W[expert_ids[p]]^T with W given in 2:4 compressed NVFP4 form
+    (batched_sparse_v7, sparse_fp4_v7.cu:374-406).
+
+    A [P,K] f16/bf16; B_comp_T [E,K/4,N] u8; Meta_T_pk [E,K/8,N] u8; scales_T [E,G,N] e4m3 bytes
+    (G = K/16 or K/8 vectorised, any divisor of K/8 otherwise); g_scales [E] f32; expert_ids [P]."""
+    dev = require_cuda(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids)
+    _check_act(A, "A")
+    _check_u8(B_comp_T, "B_comp_T"), _check_u8(Meta_T_pk, "Meta_T_pk"), _check_u8(scales_T, "scales_T")
+    P, K = A.shape
+    E, K4, N = B_comp_T.shape
+    G = scales_T.shape[1]
+    require(K4 * 4 == K and K % 8 == 0, "B_comp_T must be [E, K/4, N]")
+    require(tuple(Meta_T_pk.shape) == (E, K // 8, N), "Meta_T_pk must be [E, K/8, N]")
+    require(scales_T.shape[0] == E and scales_T.shape[2] == N and (K // 8) % G == 0, "scales_T must be [E, G, N]")
+    require(g_scales.dtype == torch.float32 and g_scales.numel() >= E and g_scales.is_contiguous(), "g_scales must be f32 [E]")
+    ids = _ids_i32(expert_ids)
+    require(ids.numel() == P, "expert_ids must have one entry per row of A")
+    out = torch.empty((P, N), dtype=_out_dtype(A, out_dtype), device=dev)
+    L = _lib.lib()
+    nws = L.b200fp4_sparse_workspace_bytes(P, E)
+    ws = workspace(dev, nws)
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_sparse_gemv(ptr(A), dtype_code(A.dtype), ptr(B_comp_T), ptr(Meta_T_pk), ptr(scales_T),
+                                         ptr(g_scales), ptr(ids), ptr(out), dtype_code(out.dtype), P, N, K, G, E,
+                                         ptr(ws), ws.numel(), stream_ptr(dev)), "batched_sparse_v7")
+    return out
+
+
+def batched_dense_v7(A, B_dense_T, scales_T, g_scales, expert_ids, *, out_dtype=None):
+    """Dense-code variant (batched_dense_v7, sparse_fp4_v7.cu:341-372): B_dense_T [E,K/2,N] u8."""
+    dev = require_cuda(A, B_dense_T, scales_T, g_scales, expert_ids)
+    _check_act(A, "A")
+    _check_u8(B_dense_T, "B_dense_T"), _check_u8(scales_T, "scales_T")
+    P, K = A.shape
+    E, K2, N = B_dense_T.shape
+    G = scales_T.shape[1]
+    require(K2 * 2 == K, "B_dense_T must be [E, K/2, N]")
+    require(scales_T.shape[0] == E and scales_T.shape[2] == N and K % G == 0 and (K // G) % 2 == 0, "scales_T must be [E, G, N]")
+    require(g_scales.dtype == torch.float32 and g_scales.numel() >= E and g_scales.is_contiguous(), "g_scales must be f32 [E]")
+    ids = _ids_i32(expert_ids)
+    require(ids.numel() == P, "expert_ids must have one entry per row of A")
+    out = torch.empty((P, N), dtype=_out_dtype(A, out_dtype), device=dev)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_dense_gemv(ptr(A), dtype_code(A.dtype), ptr(B_dense_T), ptr(scales_T), ptr(g_scales),
+                                        ptr(ids), ptr(out), dtype_code(out.dtype), P, N, K, G, E, 0, 0,
+                                        stream_ptr(dev)), "batched_dense_v7")
+    return out
+
+
+def batched_sparse_packed_v7(A, B_packed_T, g_scales, expert_ids, orig_K, *, out_dtype=None):
+    """Interleaved-tensor variant (batched_sparse_packed_v7, sparse_fp4_v7.cu:408-436):
+    B_packed_T [E, K/8, 4N] = comp0 | comp1 | meta | scale per row, one scale per 8 k."""
+    dev = require_cuda(A, B_packed_T, g_scales, expert_ids)
+    _check_act(A, "A")
+    _check_u8(B_packed_T, "B_packed_T")
+    P, K = A.shape
+    require(int(orig_K) == K, "orig_K must equal A.shape[1]")
+    E, K8, N4 = B_packed_T.shape
+    require(K8 * 8 == K and N4 % 4 == 0, "B_packed_T must be [E, K/8, 4N]")
+    N = N4 // 4
+    require(g_scales.dtype == torch.float32 and g_scales.numel() >= E and g_scales.is_contiguous(), "g_scales must be f32 [E]")
+    ids = _ids_i32(expert_ids)
+    require(ids.numel() == P, "expert_ids must have one entry per row of A")
+    out = torch.empty((P, N), dtype=_out_dtype(A, out_dtype), device=dev)
+    L = _lib.lib()
+    ws = workspace(dev, L.b200fp4_sparse_workspace_bytes(P, E))
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_sparse_packed_gemv(ptr(A), dtype_code(A.dtype), ptr(B_packed_T), ptr(g_scales), ptr(ids),
+                                                ptr(out), dtype_code(out.dtype), P, N, K, E, ptr(ws), ws.numel(),
+                                                stream_ptr(dev)), "batched_sparse_packed_v7")
+    return out
+
+
+def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
+                        w13_comp, w13_meta, w13_scale, w13_g_scales,
+                        w2_comp, w2_meta, w2_scale, w2_g_scales,
+                        inter_size, apply_router_weight_on_input, *, out_dtype=None):
+    """One MoE layer for decode (fused_sparse_moe_v7, sparse_fp4_v7.cu:607-742):
+    gate_up GEMV -> SiLU(gate)*up -> down GEMV -> router-weighted sum.
+
+    hidden_states [M,H] f16/bf16; topk_weights [M,topk] f32; topk_ids [M,topk] int; expert_map [global_E]
+    int32 or an empty tensor / None for identity; w13_* [E,H/4,2I], [E,H/8,2I], [E,G,2I], [E];
+    w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H]."""
+    dev = require_cuda(hidden_states, topk_weights, topk_ids, w13_comp, w13_meta, w13_scale, w13_g_scales,
+                       w2_comp, w2_meta, w2_scale, w2_g_scales)
+    _check_act(hidden_states, "hidden_states")
+    for t, n in ((w13_comp, "w13_comp"), (w13_meta, "w13_meta"), (w13_scale, "w13_scale"), (w2_comp, "w2_comp"),
+                 (w2_meta, "w2_meta"), (w2_scale, "w2_scale")):
+        _check_u8(t, n)
+    M, H = hidden_states.shape
+    require(topk_ids.dim() == 2 and topk_ids.shape[0] == M, "topk_ids must be [M, topk]")
+    topk = topk_ids.shape[1]
+    I = int(inter_size)
+    E = w13_comp.shape[0]
+    require(tuple(w13_comp.shape) == (E, H // 4, 2 * I), "w13_comp must be [E, H/4, 2I]")
+    require(tuple(w13_meta.shape) == (E, H // 8, 2 * I), "w13_meta must be [E, H/8, 2I]")
+    require(w13_scale.shape[0] == E and w13_scale.shape[2] == 2 * I, "w13_scale must be [E, G, 2I]")
+    require(tuple(w2_comp.shape) == (E, I // 4, H), "w2_comp must be [E, I/4, H]")
+    require(tuple(w2_meta.shape) == (E, I // 8, H), "w2_meta must be [E, I/8, H]")
+    require(w2_scale.shape[0] == E and w2_scale.shape[2] == H, "w2_scale must be [E, G, H]")
+    for g in (w13_g_scales, w2_g_scales):
+        require(g.dtype == torch.float32 and g.numel() >= E and g.is_contiguous(), "g_scales must be f32 [E]")
+    tw = topk_weights
+    if tw.dtype != torch.float32:
+        tw = tw.float()
+    tw = tw.contiguous()
+    require(tuple(tw.shape) == (M, topk), "topk_weights must be [M, topk]")
+    ids = _ids_i32(topk_ids)
+    emap = None
+    if expert_map is not None and expert_map.numel() > 0:
+        require(expert_map.is_cuda, "expert_map must be a CUDA tensor")
+        emap = expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)
+        emap = emap.contiguous()
+    out = torch.empty((M, H), dtype=_out_dtype(hidden_states, out_dtype), device=dev)
+    L = _lib.lib()
+    ws = workspace(dev, L.b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E))
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_fused_sparse_moe(
+            ptr(hidden_states), dtype_code(hidden_states.dtype), ptr(tw), ptr(ids), ptr(emap),
+            0 if emap is None else emap.numel(),
+            ptr(w13_comp), ptr(w13_meta), ptr(w13_scale), ptr(w13_g_scales), w13_scale.shape[1],
+            ptr(w2_comp), ptr(w2_meta), ptr(w2_scale), ptr(w2_g_scales), w2_scale.shape[1],
+            ptr(out), dtype_code(out.dtype), M, topk, H, I, E, 1 if apply_router_weight_on_input else 0,
+            ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_v7")
+    return out

@@ -1,0 +1,161 @@
+/*
+ * b200_nvfp4.h -- C ABI of libb200nvfp4.so: the NVFP4 hot path for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (all entry points)
+ *   - Every function returns a b200fp4Status_t (values identical to the reference's
+ *     cudaFP4Status_t, cutlass_nvfp4/cuda_fp4_gemm.h:33-42).  No function prints, synchronises
+ *     the device, reads device memory on the host or allocates device memory.
+ *   - Tensor arguments are BORROWED device pointers with explicit sizes; dtype selectors are the
+ *     B200FP4_DTYPE_* ints.  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *   - Scalars that the caller keeps on the device (global scales, alpha) are passed as device
+ *     pointers so a call sequence can be captured into a CUDA graph.
+ *   - Work is enqueued on `stream`; a non-zero status means nothing was enqueued, except
+ *     B200FP4_STATUS_EXECUTION_FAILED which reports a launch error from the CUDA runtime.
+ *   - Packed E2M1 codes: element 2i in the low nibble, 2i+1 in the high nibble of byte i
+ *     (patch_nvfp4_utils_sw_e2m1.py:48-63).  Block scales are E4M3 bytes, one per 16 elements
+ *     along K.
+ *
+ * Each declaration names the reference interface it replaces (path:line inside the
+ * Avarok-Cybersecurity/dgx-vllm tree; "vllm/..." = the vLLM tree that project patches).
+ */
+#ifndef B200_NVFP4_H_
+#define B200_NVFP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200FP4_API
+#else
+#define B200FP4_API __attribute__((visibility("default")))
+#endif
+
+/* Replaces cudaFP4Status_t, cutlass_nvfp4/cuda_fp4_gemm.h:33-42 (same numeric values). */
+typedef enum {
+  B200FP4_STATUS_SUCCESS = 0,
+  B200FP4_STATUS_NOT_INITIALIZED = 1,
+  B200FP4_STATUS_ALLOC_FAILED = 3,
+  B200FP4_STATUS_INVALID_VALUE = 7,
+  B200FP4_STATUS_ARCH_MISMATCH = 8,
+  B200FP4_STATUS_EXECUTION_FAILED = 13,
+  B200FP4_STATUS_INTERNAL_ERROR = 14,
+  B200FP4_STATUS_NOT_SUPPORTED = 15
+} b200fp4Status_t;
+
+enum { B200FP4_DTYPE_F16 = 0, B200FP4_DTYPE_BF16 = 1, B200FP4_DTYPE_F32 = 2 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Utilities.  Replace cudaFP4GetErrorString / cudaFP4GetVersion / cudaFP4GetVersionString /
+ * cudaFP4HasHardwareAcceleration, cutlass_nvfp4/cuda_fp4_gemm.h:124-147.
+ * ------------------------------------------------------------------------------------------- */
+B200FP4_API const char* b200fp4_get_error_string(int status);
+B200FP4_API int b200fp4_version(void);
+B200FP4_API const char* b200fp4_version_string(void);
+/* 1 when the current device is compute capability 10.x (tcgen05 / native E2M1 cvt), else 0. */
+B200FP4_API int b200fp4_has_hardware_acceleration(void);
+/* Number of kernels this library has launched in the calling process (monotonic counter). */
+B200FP4_API uint64_t b200fp4_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Part 1 -- activation quantizer.
+ * Replaces the scaled_fp4_quant op (vllm/_custom_ops.py:1600-1671) whose device code the
+ * reference patches with fp32_vec8_to_e2m1 / fp32_vec16_to_e2m1
+ * (patch_nvfp4_utils_sw_e2m1.py:105-131,168-193,236-274); arithmetic order is that of
+ * ref_nvfp4_quant as called at fix_nvfp4_emulation_backend.py:72.
+ *
+ *   x            [M, K] bf16 or f16 (in_dtype), row stride ldx elements, K % 16 == 0
+ *   global_scale device pointer to one f32 (= 448*6/amax, vLLM's input_global_scale)
+ *   codes        [M, K/2] u8 out
+ *   sf           e4m3 out: linear [M, K/16], or, when sf_swizzled != 0, the padded 128x4 tile
+ *                layout of b200fp4_sf_swizzled_bytes(M, K/16) bytes.  Padding bytes of the
+ *                swizzled layout are written as zero by this call.
+ * ------------------------------------------------------------------------------------------- */
+B200FP4_API size_t b200fp4_sf_swizzled_bytes(int64_t rows, int64_t k_blocks);
+B200FP4_API int b200fp4_quantize(const void* x, int in_dtype, int64_t M, int64_t K, int64_t ldx,
+                                 const float* global_scale, void* codes, void* sf, int sf_swizzled,
+                                 void* stream);
+
+/* Per-expert variant.  Replaces scaled_fp4_experts_quant(output, output_scales, input,
+ * input_global_scale, expert_offsets, blockscale_offsets), vllm/_custom_ops.py:1674-1733 (one of
+ * the five NVFP4 sources the reference force-compiles, cmake_patch_gb10_nvfp4_v6_full_kernels.sh:58-62).
+ * Rows [expert_offsets[e], expert_offsets[e+1]) use global_scales[e]; their scale factors go to
+ * swizzled rows starting at blockscale_offsets[e] (a multiple of 128).  sf must hold
+ * sf_rows_padded * ceil(K/64)*4 bytes and is fully written (padding = 0).
+ * If silu_mul != 0 the input is [M, 2K] and SiLU(x[:, :K]) * x[:, K:] is quantized instead
+ * (silu_and_mul_scaled_fp4_experts_quant, same file list). */
+B200FP4_API int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, int64_t K,
+                                         const float* global_scales, const int32_t* expert_offsets,
+                                         const int32_t* blockscale_offsets, int32_t num_experts,
+                                         int64_t sf_rows_padded, int silu_mul, void* codes, void* sf,
+                                         void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Part 3 -- 2:4-sparse / dense NVFP4 batched GEMV for MoE decode.
+ * Replace the pybind functions of sparse_fp4_kernel/sparse_fp4_v7.cu:744-749.
+ *
+ * Common arguments
+ *   A          [P, K] activations (a_dtype f16 or bf16), one row per (token, expert) pair
+ *   scales_T   [E, G, N] e4m3, G = K/16 or K/8 (one scale per K/G consecutive k)
+ *   g_scales   [E] f32
+ *   expert_ids [P] i32; ids outside [0, E) produce a zero row (the reference indexes out of
+ *              bounds there)
+ *   out        [P, N] (out_dtype f16 or bf16)
+ *   workspace  b200fp4_sparse_workspace_bytes(P, E) bytes of scratch, 256-byte aligned
+ * N % 16 == 0 selects the vectorised kernel; other N fall back to a scalar kernel.
+ * ------------------------------------------------------------------------------------------- */
+B200FP4_API size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t E);
+
+/* batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids),
+ * sparse_fp4_v7.cu:374-406.  B_comp_T [E, K/4, N], Meta_T_pk [E, K/8, N]. */
+B200FP4_API int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B_comp_T,
+                                    const uint8_t* Meta_T_pk, const uint8_t* scales_T,
+                                    const float* g_scales, const int32_t* expert_ids, void* out,
+                                    int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G,
+                                    int64_t E, void* workspace, size_t workspace_bytes, void* stream);
+
+/* batched_dense_v7(A, B_dense_T, scales_T, g_scales, expert_ids), sparse_fp4_v7.cu:341-372.
+ * B_dense_T [E, K/2, N]. */
+B200FP4_API int b200fp4_dense_gemv(const void* A, int a_dtype, const uint8_t* B_dense_T,
+                                   const uint8_t* scales_T, const float* g_scales,
+                                   const int32_t* expert_ids, void* out, int out_dtype, int64_t P,
+                                   int64_t N, int64_t K, int64_t G, int64_t E, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/* batched_sparse_packed_v7(A, B_packed_T, g_scales, expert_ids, orig_K), sparse_fp4_v7.cu:408-436.
+ * B_packed_T [E, K/8, 4N]: per row comp0 | comp1 | meta | scale, one scale per 8 k. */
+B200FP4_API int b200fp4_sparse_packed_gemv(const void* A, int a_dtype, const uint8_t* B_packed_T,
+                                           const float* g_scales, const int32_t* expert_ids,
+                                           void* out, int out_dtype, int64_t P, int64_t N, int64_t K,
+                                           int64_t E, void* workspace, size_t workspace_bytes,
+                                           void* stream);
+
+/* fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map, w13_*, w2_*, inter_size,
+ * apply_router_weight_on_input), sparse_fp4_v7.cu:607-742: gate_up GEMV -> SiLU(gate)*up ->
+ * down GEMV -> router-weighted sum per token.
+ *   hidden      [M, H] (h_dtype)            topk_weights [M, topk] f32   topk_ids [M, topk] i32
+ *   expert_map  [global_E] i32 or NULL (identity); entries < 0 mark experts that are not local:
+ *               such pairs contribute nothing (the reference does not handle them)
+ *   w13_*       comp [E, H/4, 2I], meta [E, H/8, 2I], scale [E, G13, 2I], g [E]
+ *   w2_*        comp [E, I/4, H],  meta [E, I/8, H],  scale [E, G2, H],  g [E]
+ *   out         [M, H] (out_dtype)
+ *   workspace   b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E) bytes
+ * apply_router_weight_on_input != 0 sums the expert outputs unweighted, exactly as the reference
+ * kernel does (sparse_fp4_v7.cu:592-594). */
+B200FP4_API size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I,
+                                                     int64_t E);
+B200FP4_API int b200fp4_fused_sparse_moe(
+    const void* hidden, int h_dtype, const float* topk_weights, const int32_t* topk_ids,
+    const int32_t* expert_map, int64_t global_E, const uint8_t* w13_comp, const uint8_t* w13_meta,
+    const uint8_t* w13_scale, const float* w13_g, int64_t G13, const uint8_t* w2_comp,
+    const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out,
+    int out_dtype, int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
+    int apply_router_weight_on_input, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_NVFP4_H_ */

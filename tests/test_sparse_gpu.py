@@ -1,0 +1,140 @@
+"""GPU parity of the 2:4-sparse MoE GEMV ops (through the C ABI) against the oracle.
+Tolerance: max|diff| / max|ref| <= 1e-2 against the fp32 dequantize-then-matmul result."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import oracle_quantize_fn, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _rand_sparse(E, N, K, G, seed):
+    rng = np.random.default_rng(seed)
+    comp = rng.integers(0, 256, (E, K // 4, N), dtype=np.uint8)
+    meta = rng.integers(0, 256, (E, K // 8, N), dtype=np.uint8)
+    scale = rng.integers(56, 120, (E, G, N), dtype=np.uint8)      # as bench_v7_scaled.py:153
+    g = (rng.random(E) * 1e-3 + 1e-4).astype(np.float32)
+    return comp, meta, scale, g
+
+
+def _cuda(*arrs):
+    return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrs]
+
+
+@pytest.mark.parametrize("E,N,K,G,P", [
+    (4, 512, 64, 8, 2),          # the reference's own validation shape (bench_v7_scaled.py:133)
+    (4, 512, 64, 4, 3),
+    (6, 1024, 2048, 128, 9),     # gate_up projection of the MoE configuration
+    (6, 2048, 512, 32, 9),       # down projection
+    (3, 144, 96, 6, 5),          # N not a multiple of the 128-column slab
+    (3, 40, 48, 6, 4),           # N % 16 != 0 -> scalar kernel
+    (2, 64, 64, 2, 3),           # one scale per 32 k -> scalar kernel
+])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_batched_sparse_v7(E, N, K, G, P, dtype):
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    comp, meta, scale, g = _rand_sparse(E, N, K, G, seed=E * N + K)
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, E, P).astype(np.int32)
+    A = torch.randn(P, K, generator=torch.Generator().manual_seed(2)).to(dtype)
+    out = sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta, scale, g, ids))
+    assert out.dtype == dtype and tuple(out.shape) == (P, N)
+    ref = oracle.batched_sparse_gemv(A.float().numpy(), comp, meta, scale, g, ids)
+    assert rel_err(to_np(out), ref) < TOL
+    out2 = sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta, scale, g, ids))
+    assert torch.equal(out, out2)                                  # deterministic
+
+
+def test_many_tokens_per_expert_and_unmapped_ids():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, N, K, G, P = 3, 256, 256, 16, 23
+    comp, meta, scale, g = _rand_sparse(E, N, K, G, seed=7)
+    ids = np.array([0] * 11 + [2] * 6 + [-1, 5, 1, 1, 1, -7], np.int32)   # >4 per expert, invalid ids
+    A = torch.randn(P, K, generator=torch.Generator().manual_seed(3)).to(torch.float16)
+    out = to_np(sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta, scale, g, ids)))
+    safe = np.where((ids >= 0) & (ids < E), ids, -1)
+    ref = oracle.batched_sparse_gemv(A.float().numpy(), comp, meta, scale, g, safe)
+    assert rel_err(out, ref) < TOL
+    assert np.all(out[safe < 0] == 0)
+
+
+def test_dense_and_packed_variants():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, N, K, P = 3, 128, 128, 4
+    rng = np.random.default_rng(11)
+    dense = rng.integers(0, 256, (E, K // 2, N), dtype=np.uint8)
+    scale = rng.integers(56, 120, (E, K // 16, N), dtype=np.uint8)
+    g = (rng.random(E) * 1e-3 + 1e-4).astype(np.float32)
+    ids = np.array([2, 0, 1, 2], np.int32)
+    A = torch.randn(P, K, generator=torch.Generator().manual_seed(4)).to(torch.float16)
+    out = sp7.batched_dense_v7(A.cuda(), *_cuda(dense, scale, g, ids))
+    assert rel_err(to_np(out), oracle.batched_dense_gemv(A.float().numpy(), dense, scale, g, ids)) < TOL
+    comp, meta, scale8, g = _rand_sparse(E, N, K, K // 8, seed=12)
+    packed = np.concatenate([comp[:, 0::2], comp[:, 1::2], meta, scale8], axis=2)      # [E, K/8, 4N]
+    out = sp7.batched_sparse_packed_v7(A.cuda(), *_cuda(packed, g, ids), K)
+    assert rel_err(to_np(out), oracle.batched_sparse_gemv(A.float().numpy(), comp, meta, scale8, g, ids)) < TOL
+
+
+def _moe_case(E, H, I, B, topk, seed, dtype=torch.bfloat16):
+    from dgx_vllm_b200 import synth
+    w13 = synth.make_sparse_experts(E, 2 * I, H, seed, "cpu", oracle_quantize_fn)
+    w2 = synth.make_sparse_experts(E, H, I, seed + 1, "cpu", oracle_quantize_fn)
+    tw, ids = synth.make_routing(B, E, topk, seed + 2, "cpu")
+    hidden = synth.make_hidden(B, H, seed + 3, "cpu", dtype)
+    return w13, w2, tw, ids, hidden
+
+
+def _run_fused(w13, w2, tw, ids, hidden, I, emap=None, on_input=False):
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    emap_t = torch.empty(0, dtype=torch.int32, device="cuda") if emap is None else torch.from_numpy(emap).cuda()
+    return sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), emap_t, *c(w13), *c(w2), I, on_input)
+
+
+def _ref_fused(w13, w2, tw, ids, hidden, I, emap=None, on_input=False):
+    n = lambda d: tuple(d[k].numpy() for k in ("comp_T", "meta_T", "scale_T", "g_scales"))
+    return oracle.fused_sparse_moe(hidden.float().numpy(), tw.numpy(), ids.numpy(), emap, n(w13), n(w2), I,
+                                   apply_router_weight_on_input=on_input, round_fp16=False)
+
+
+@pytest.mark.parametrize("B", [1, 8, 32])
+def test_fused_moe_layer(B):
+    # the MoE decode configuration at reduced expert count (shapes per expert are the real ones)
+    E, H, I, topk = 16, 2048, 512, 10
+    case = _moe_case(E, H, I, B, topk, seed=B)
+    out = _run_fused(*case, I)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (B, H)
+    ref = _ref_fused(*case, I)
+    assert rel_err(to_np(out), ref) < TOL
+    assert torch.equal(out, _run_fused(*case, I))
+
+
+def test_fused_moe_expert_map_and_flags():
+    E_local, E_global, H, I, B, topk = 4, 8, 256, 128, 5, 3
+    w13, w2, _, _, hidden = _moe_case(E_local, H, I, B, topk, seed=9, dtype=torch.float16)
+    from dgx_vllm_b200 import synth
+    tw, ids = synth.make_routing(B, E_global, topk, 10, "cpu")
+    emap = np.array([-1, 0, -1, 1, 2, -1, 3, -1], np.int32)       # half of the global experts are local
+    out = _run_fused(w13, w2, tw, ids, hidden, I, emap)
+    ref = _ref_fused(w13, w2, tw, ids, hidden, I, emap)
+    assert out.dtype == torch.float16
+    assert rel_err(to_np(out), ref) < TOL
+    out = _run_fused(w13, w2, tw, ids, hidden, I, emap, on_input=True)
+    ref = _ref_fused(w13, w2, tw, ids, hidden, I, emap, on_input=True)
+    assert rel_err(to_np(out), ref) < TOL
+
+
+def test_argument_validation():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    comp, meta, scale, g = _rand_sparse(2, 64, 64, 4, seed=1)
+    A = torch.randn(2, 64).half()
+    ids = np.array([0, 1], np.int32)
+    with pytest.raises(RuntimeError):
+        sp7.batched_sparse_v7(A, *_cuda(comp, meta, scale, g, ids))               # A on the CPU
+    with pytest.raises(RuntimeError):
+        sp7.batched_sparse_v7(A.cuda().float(), *_cuda(comp, meta, scale, g, ids))   # wrong dtype
+    with pytest.raises(RuntimeError):
+        sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta[:, :4], scale, g, ids))    # wrong meta shape
