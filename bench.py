@@ -1,0 +1,348 @@
+#!/usr/bin/env python3
+"""Benchmark of the NVFP4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--batch B]
+
+Headline line (one JSON object on stdout, printed by rank 0): NVFP4 MoE-layer tokens/s on the
+sparse 2:4 MoE GEMV decode configuration -- 512 experts, hidden 2048, moe_intermediate 512, top-10
+routing from softmax of N(0,1) logits, B tokens per GPU (default 32).  A step is one MoE layer over
+one batch.  With N > 1 the layer is expert-parallel (512/N experts per GPU, all-to-all dispatch and
+combine over NCCL) and every GPU brings its own batch (weak scaling).
+
+  value      device-timed whole-job tokens/s, inputs resident in HBM
+  e2e        the same through the public op with host buffers (H2D of activations/routing and D2H
+             of the result inside the timed region)
+  roofline   sparse GEMV kernel: algorithmic weight+activation bytes per launch / CUDA-event
+             duration of that launch, against the measured HBM copy bandwidth
+  cpu_baseline  the reference's dequantize-to-bf16 emulation (oracle port, torch on the host cores)
+
+`--impl reference` times that CPU emulation as the main measurement instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+E_TOTAL, HIDDEN, INTER, TOPK = 512, 2048, 512, 10
+BYTES_PER_EXPERT_GATE_UP = 2 * INTER * HIDDEN * 7 // 16          # comp 1/4 + meta 1/8 + scale 1/16 B per weight
+BYTES_PER_EXPERT_DOWN = HIDDEN * INTER * 7 // 16
+N_ROUTINGS = 8
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi; only samples whose timestamp falls
+    inside the window marked by begin()/end() (the timed regions) are reported."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.idx = gpu_index
+        self.t0 = self.t1 = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "20", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
+
+    def stop(self):
+        import datetime
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if self.t0 is not None and not (self.t0 - 0.02 <= ts <= (self.t1 or ts) + 0.02):
+                    continue
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def build_case(dev, e_local: int, batch: int, rank: int):
+    import torch
+    from dgx_vllm_b200 import scaled_fp4_quant, synth
+
+    def qfn(w, gs):
+        c, s = scaled_fp4_quant(w, gs, is_sf_swizzled_layout=False)
+        return c, s.view(torch.uint8)
+
+    w13 = synth.make_sparse_experts(e_local, 2 * INTER, HIDDEN, 1000 + rank, dev, qfn)
+    w2 = synth.make_sparse_experts(e_local, HIDDEN, INTER, 2000 + rank, dev, qfn)
+    batches = []
+    for i in range(N_ROUTINGS):
+        tw, ids = synth.make_routing(batch, E_TOTAL, TOPK, 10 * rank + i, dev)
+        hidden = synth.make_hidden(batch, HIDDEN, 100 + 10 * rank + i, dev)
+        batches.append((hidden, tw, ids))
+    return w13, w2, batches
+
+
+def cpu_baseline(batch: int, max_seconds: float = 25.0):
+    """Times the reference's dequantize-to-bf16 emulation of the same MoE layer on the host cores.
+    The sample is one batch routed over a reduced expert table (same per-expert shapes), repeated
+    until ~max_seconds of CPU work have been spent."""
+    import torch
+    from dgx_vllm_b200 import synth
+    from oracle import emulation
+    import oracle
+    import numpy as np
+
+    def qfn(w, gs):
+        bits = w.contiguous().view(torch.int16).numpy().view(np.uint16)
+        c, s = oracle.quantize_bf16(bits, float(gs[0]))
+        return torch.from_numpy(c), torch.from_numpy(s)
+
+    e_cpu = 64                                     # experts materialised on the host for the sample
+    w13 = synth.make_sparse_experts(e_cpu, 2 * INTER, HIDDEN, 1, "cpu", qfn)
+    w2 = synth.make_sparse_experts(e_cpu, HIDDEN, INTER, 2, "cpu", qfn)
+    tw, ids = synth.make_routing(batch, E_TOTAL, TOPK, 3, "cpu")
+    uniq_full = int(ids.unique().numel())
+    # remap the routed experts onto the materialised ones without merging them beyond e_cpu:
+    # the active-expert count per step (the cost driver) is min(unique, e_cpu); scale the time up.
+    ids_c = (ids % e_cpu).to(torch.int32)
+    uniq_cpu = int(ids_c.unique().numel())
+    hidden = synth.make_hidden(batch, HIDDEN, 4, "cpu")
+    emulation.moe_layer_emulation(hidden[:1], tw[:1], ids_c[:1], w13, w2, INTER)        # warm-up
+    times = []
+    t_end = time.perf_counter() + max_seconds
+    while len(times) < 5 and (time.perf_counter() < t_end or not times):
+        t0 = time.perf_counter()
+        emulation.moe_layer_emulation(hidden, tw, ids_c, w13, w2, INTER)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times) * (uniq_full / max(uniq_cpu, 1))
+    return {"value": batch / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": (f"one batch of {batch} tokens, {uniq_cpu} active experts materialised on the host "
+                       f"(of {uniq_full} routed), time scaled by {uniq_full}/{uniq_cpu}; "
+                       f"median of {len(times)} runs, per-call weight dequantisation included")}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cb = cpu_baseline(args.batch, max_seconds=20.0 * max(1, min(args.steps, 3)))
+    ms = args.batch / cb["value"] * 1e3
+    line = {"impl": "reference", "metric": "NVFP4 MoE-layer tokens/s", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": config_dict(args),
+            "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                                        "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "host_threads": torch.get_num_threads()}
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args):
+    return {"workload": "sparse 2:4 NVFP4 MoE GEMV decode layer (BASELINE configs[2])", "experts": E_TOTAL,
+            "hidden": HIDDEN, "moe_intermediate": INTER, "topk": TOPK, "batch_per_gpu": args.batch,
+            "parallelism": f"ep{args.gpus}" if args.gpus > 1 else "single",
+            "l2": f"routed expert weights per step exceed the 126 MB L2 at batch>=16; routing rotates over "
+                  f"{N_ROUTINGS} seeded batches and a 256 MiB buffer is rewritten between timed steps of the "
+                  f"per-kernel (roofline) loop"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from dgx_vllm_b200 import _lib, sparse_fp4_v7 as sp7
+    from dgx_vllm_b200.moe_ep import ExpertParallelMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    if L.b200fp4_has_hardware_acceleration() != 1:
+        raise SystemExit("bench.py needs an sm_100 device")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e_local = E_TOTAL // world
+    w13, w2, batches = build_case(dev, e_local, args.batch, rank)
+    layer = ExpertParallelMoE(E_TOTAL, INTER, w13, w2)
+    B = args.batch
+    hbm_peak, peak_kind = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i):
+        h, tw, ids = batches[i % N_ROUTINGS]
+        return layer.forward(h, tw, ids)
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+
+    # ---- value: K steps back to back, device-timed
+    sampler.begin()
+    n0 = L.b200fp4_launch_count()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = int(L.b200fp4_launch_count() - n0)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = B * world / (ms_step * 1e-3)
+
+    # ---- roofline: per-launch duration of the two GEMV kernels, cold L2 (flush between steps)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    uniq = []
+    for i in range(args.steps):
+        h, tw, ids = batches[i % N_ROUTINGS]
+        emap = layer.expert_map(dev)
+        flush.zero_()
+        for e in evs[i]:
+            e.record()      # creates the underlying CUDA events; the library re-records them
+        L.b200fp4_fused_moe_profile_events(evs[i][0].cuda_event, evs[i][1].cuda_event, evs[i][2].cuda_event)
+        if world == 1:
+            step(i)
+            uniq.append(int(ids.unique().numel()))
+        else:
+            # local part only: the GEMV kernels see the tokens of all ranks; count this rank's experts
+            k = ("comp_T", "meta_T", "scale_T", "g_scales")
+            sp7.fused_sparse_moe_v7(h, tw, ids, emap, *[w13[x] for x in k], *[w2[x] for x in k], INTER, False)
+            m = emap[ids.long()]
+            uniq.append(int(m[m >= 0].unique().numel()))
+        L.b200fp4_fused_moe_profile_events(0, 0, 0)
+    torch.cuda.synchronize()
+    t_gu = [evs[i][0].elapsed_time(evs[i][1]) * 1e-3 for i in range(args.steps)]
+    t_dn = [evs[i][1].elapsed_time(evs[i][2]) * 1e-3 for i in range(args.steps)]
+    pairs = B * TOPK
+    # algorithmic bytes per launch: weights of the unique experts + activations in/out per pair
+    b_gu = [u * BYTES_PER_EXPERT_GATE_UP + pairs * (HIDDEN * 2 + INTER * 2) for u in uniq]
+    b_dn = [u * BYTES_PER_EXPERT_DOWN + pairs * (INTER * 2 + HIDDEN * 4) for u in uniq]
+    ach = (sum(b_gu) + sum(b_dn)) / (sum(t_gu) + sum(t_dn)) / 1e9
+    roofline = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth",
+                "kernel": "sparse_gemv_kernel (gate_up+SiLU and down launches of one layer)",
+                "per_launch_us": {"gate_up": statistics.mean(t_gu) * 1e6, "down": statistics.mean(t_dn) * 1e6},
+                "algorithmic_bytes_per_step": (sum(b_gu) + sum(b_dn)) / args.steps,
+                "gate_up_GBps": sum(b_gu) / sum(t_gu) / 1e9, "down_GBps": sum(b_dn) / sum(t_dn) / 1e9,
+                "unique_experts_mean": statistics.mean(uniq)}
+    traffic_file = os.path.join(ROOT, "profiles", "sparse_gemv_traffic.json")
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as f:
+            roofline["traffic"] = json.load(f).get("dram_bytes_per_step")
+
+    # ---- e2e: host buffers in, host result out, through the public op
+    host = []
+    for h, tw, ids in batches:
+        host.append((h.cpu().pin_memory(), tw.cpu().pin_memory(), ids.cpu().pin_memory()))
+    out_host = torch.empty(B, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        hh, hw, hi = host[i % N_ROUTINGS]
+        h = hh.to(dev, non_blocking=True)
+        tw = hw.to(dev, non_blocking=True)
+        ids = hi.to(dev, non_blocking=True)
+        out = layer.forward(h, tw, ids)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    e2e_val = B * world * args.steps / float(dt.item())
+    sampler.end()
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = B * HIDDEN * 2 + B * TOPK * 8
+    d2h = B * HIDDEN * 2
+
+    if rank == 0:
+        line = {"metric": "NVFP4 MoE-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16 products, f32 accumulate (NVFP4 weights, bf16 activations)",
+                "data": "synthetic", "config": config_dict(args), "roofline": roofline,
+                "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "gpu_launches": launches, "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(B)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

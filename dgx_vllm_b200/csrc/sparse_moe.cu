@@ -501,6 +501,9 @@ __global__ void weighted_reduce_kernel(const float* __restrict__ down, const flo
 
 // ------------------------------------------------------------------------------------------ host
 
+// Optional CUDA events recorded around the two GEMV launches of the fused layer (benchmark hook).
+cudaEvent_t g_prof_events[3] = {nullptr, nullptr, nullptr};
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 size_t plan_bytes(int64_t P, int64_t E) {
@@ -690,6 +693,12 @@ extern "C" int b200fp4_sparse_packed_gemv(const void* A, int a_dtype, const uint
   return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, K / 8, E, workspace, workspace_bytes, stream);
 }
 
+extern "C" void b200fp4_fused_moe_profile_events(void* before_gate_up, void* after_gate_up, void* after_down) {
+  g_prof_events[0] = (cudaEvent_t)before_gate_up;
+  g_prof_events[1] = (cudaEvent_t)after_gate_up;
+  g_prof_events[2] = (cudaEvent_t)after_down;
+}
+
 extern "C" size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
   const int64_t P = M * topk;
@@ -735,11 +744,14 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
   float* down = reinterpret_cast<float*>(ws + plan_bytes(P, E) + align_up((size_t)P * I * sizeof(__half), 256));
 
   moe_plan_kernel<<<1, kPlanThreads, 0, st>>>(topk_ids, (int)P, expert_map, (int)global_E, (int)E, plan);
+  if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
   rc = run_projection(w13, plan, hidden, h_dtype == B200FP4_DTYPE_BF16, H, (int)topk, act, B200FP4_DTYPE_F16, I, P,
                       2 * I, H, G13, E, (int)I, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
   rc = run_projection(w2, plan, act, 0, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);
   weighted_reduce_kernel<<<grid, 256, 0, st>>>(down, topk_weights, plan.mapped, out, out_dtype, (int)M, (int)topk,
                                                (int)H, apply_router_weight_on_input ? 1 : 0);

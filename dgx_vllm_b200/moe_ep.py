@@ -1,0 +1,95 @@
+"""Expert-parallel MoE decode layer: E/G experts per GPU, token dispatch and combine with one
+all-to-all each way over NCCL (NVLink / NVSwitch), local compute by the fused sparse MoE op.
+
+The reference has no multi-GPU code of its own (it serves with tensor parallelism through vLLM);
+this layout is the one the path's shard rule prescribes: experts [r*E/G, (r+1)*E/G) live on rank r.
+
+Dispatch uses fixed-capacity slots so that no host round trip (split-size exchange + .tolist())
+sits on the decode path and the step stays CUDA-graph friendly: every rank sends each peer one
+record per local token -- the token's activation row, its top-k global expert ids and router
+weights packed in one byte buffer -- and the receiving rank masks the experts it does not own
+through `expert_map` (-1 entries are skipped by the GEMV plan kernel, so foreign pairs cost no
+weight traffic).  Combine returns one partial output row per (source token, owner rank); the
+source rank adds the G partial rows in fp32.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def expert_map_for_rank(global_E: int, world: int, rank: int, device) -> torch.Tensor:
+    """global expert id -> local id on `rank`, -1 for experts owned elsewhere."""
+    per = global_E // world
+    m = torch.full((global_E,), -1, dtype=torch.int32)
+    m[rank * per:(rank + 1) * per] = torch.arange(per, dtype=torch.int32)
+    return m.to(device)
+
+
+def pack_records(hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+    """[B,H] act + [B,topk] i32 ids + [B,topk] f32 weights -> [B, H*2 + topk*8] bytes."""
+    B = hidden.shape[0]
+    return torch.cat((hidden.contiguous().view(torch.uint8).reshape(B, -1),
+                      topk_ids.to(torch.int32).contiguous().view(torch.uint8).reshape(B, -1),
+                      topk_w.to(torch.float32).contiguous().view(torch.uint8).reshape(B, -1)), dim=1)
+
+
+def unpack_records(rec: torch.Tensor, H: int, topk: int, dtype: torch.dtype):
+    n = rec.shape[0]
+    hb = H * 2
+    hidden = rec[:, :hb].contiguous().view(dtype).reshape(n, H)
+    ids = rec[:, hb:hb + topk * 4].contiguous().view(torch.int32).reshape(n, topk)
+    w = rec[:, hb + topk * 4:].contiguous().view(torch.float32).reshape(n, topk)
+    return hidden, w, ids
+
+
+class ExpertParallelMoE:
+    """One MoE layer sharded over the ranks of `group`.
+
+    local_moe_fn(hidden [T,H], topk_w [T,topk] f32, topk_ids [T,topk] i32 (global ids),
+                 expert_map [global_E] i32) -> [T,H]
+    computes the contribution of this rank's experts; by default it is the CUDA fused op over
+    `w13` / `w2` (dicts with comp_T, meta_T, scale_T, g_scales for the local experts)."""
+
+    def __init__(self, global_E: int, inter: int, w13: Optional[dict], w2: Optional[dict], group=None,
+                 local_moe_fn: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if global_E % self.world != 0:
+            raise RuntimeError("the number of experts must be divisible by the number of ranks")
+        self.global_E = global_E
+        self.inter = inter
+        self.w13, self.w2 = w13, w2
+        self._emap = None
+        self._fn = local_moe_fn or self._cuda_local
+
+    def _cuda_local(self, hidden, topk_w, topk_ids, emap):
+        from . import sparse_fp4_v7 as sp7
+        k = ("comp_T", "meta_T", "scale_T", "g_scales")
+        return sp7.fused_sparse_moe_v7(hidden, topk_w, topk_ids, emap, *[self.w13[x] for x in k],
+                                       *[self.w2[x] for x in k], self.inter, False)
+
+    def expert_map(self, device) -> torch.Tensor:
+        if self._emap is None or self._emap.device != device:
+            self._emap = expert_map_for_rank(self.global_E, self.world, self.rank, device)
+        return self._emap
+
+    def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        B, H = hidden.shape
+        topk = topk_ids.shape[1]
+        emap = self.expert_map(hidden.device)
+        if self.world == 1:
+            return self._fn(hidden, topk_w, topk_ids, emap)
+        G = self.world
+        rec = pack_records(hidden, topk_w, topk_ids)                       # [B, R]
+        send = rec.unsqueeze(0).expand(G, B, rec.shape[1]).contiguous()    # one slot block per peer
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv.view(G * B, -1), send.view(G * B, -1), group=self.group)     # dispatch
+        h_all, w_all, ids_all = unpack_records(recv.view(G * B, -1), H, topk, hidden.dtype)
+        part = self._fn(h_all, w_all, ids_all, emap)                       # [G*B, H] partial rows
+        back = torch.empty_like(part)
+        dist.all_to_all_single(back, part.contiguous(), group=self.group)  # combine
+        return back.view(G, B, H).float().sum(0).to(hidden.dtype)

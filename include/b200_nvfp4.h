@@ -155,6 +155,13 @@ B200FP4_API int b200fp4_fused_sparse_moe(
     int out_dtype, int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
     int apply_router_weight_on_input, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Benchmark hook (no counterpart in the reference): when the three cudaEvent_t handles are non-NULL,
+ * b200fp4_fused_sparse_moe records them on its stream before the gate_up GEMV, between the two
+ * GEMVs and after the down GEMV, so a caller can time the two dominant kernels inside a fused
+ * call.  Pass NULLs to switch it off.  Process-global, not thread-safe. */
+B200FP4_API void b200fp4_fused_moe_profile_events(void* before_gate_up, void* after_gate_up,
+                                                  void* after_down);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,136 @@
+"""CPU-side checks: the C ABI library loads and exports every declared symbol; host-side logic
+(synthetic generators, record packing, expert-parallel dispatch/combine over gloo)."""
+import os
+import re
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import oracle_quantize_fn, rel_err
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from dgx_vllm_b200 import _lib
+    hdr = open(os.path.join(ROOT, "include", "b200_nvfp4.h")).read()
+    declared = set(re.findall(r"\b(b200fp4_[a-z0-9_]+)\s*\(", hdr))
+    assert declared, "no declarations found"
+    L = _lib.lib()
+    for name in declared:
+        assert hasattr(L, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    assert L.b200fp4_version() >= 100
+    assert b"success" in L.b200fp4_get_error_string(0)
+    assert L.b200fp4_sf_swizzled_bytes(200, 12) == oracle.sf_swizzled_bytes(200, 12)
+    assert L.b200fp4_sparse_workspace_bytes(320, 512) > 0
+
+
+def test_no_cpu_fallback():
+    from dgx_vllm_b200 import scaled_fp4_quant, sparse_fp4_v7
+    with pytest.raises(RuntimeError):
+        scaled_fp4_quant(torch.zeros(4, 16, dtype=torch.bfloat16), torch.ones(1))
+    with pytest.raises(RuntimeError):
+        sparse_fp4_v7.batched_sparse_v7(torch.zeros(1, 16).half(), torch.zeros(1, 4, 16, dtype=torch.uint8),
+                                        torch.zeros(1, 2, 16, dtype=torch.uint8), torch.zeros(1, 1, 16, dtype=torch.uint8),
+                                        torch.ones(1), torch.zeros(1, dtype=torch.int32))
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "dgx_vllm_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(import|from)\s+oracle\b", src, re.M), f
+
+
+def test_synth_sparse_experts_are_2of4_and_consistent():
+    from dgx_vllm_b200 import synth
+    w = synth.make_sparse_experts(2, 32, 64, 0, "cpu", oracle_quantize_fn)
+    assert tuple(w["comp_T"].shape) == (2, 16, 32) and tuple(w["meta_T"].shape) == (2, 8, 32)
+    meta = w["meta_T"].numpy()
+    i0, i1, i2, i3 = meta & 3, (meta >> 2) & 3, (meta >> 4) & 3, (meta >> 6) & 3
+    assert np.all(i0 < i1) and np.all(i2 < i3)                    # two distinct, sorted positions per group
+    W = oracle.sparse_expand(w["comp_T"][0].numpy(), meta[0], w["scale_T"][0].numpy(), float(w["g_scales"][0]))
+    assert np.all((W.reshape(32, 16, 4) != 0).sum(-1) <= 2)
+    assert abs(np.abs(W).max() - 0.02 * 4) < 0.06                 # ~N(0, 0.02) magnitudes survive quantization
+
+
+def test_routing_generators():
+    from dgx_vllm_b200 import synth
+    w, ids = synth.make_routing(16, 64, 10, 0, "cpu")
+    assert ids.dtype == torch.int32 and w.dtype == torch.float32
+    assert torch.allclose(w.sum(-1), torch.ones(16), atol=1e-5)
+    assert all(len(set(r.tolist())) == 10 for r in ids)
+    w, ids = synth.make_routing(256, 64, 10, 0, "cpu", zipf=1.1)
+    counts = torch.bincount(ids.flatten().long(), minlength=64).float()
+    assert counts.max() > 3 * counts.median()                     # skewed popularity
+    assert all(len(set(r.tolist())) == 10 for r in ids)
+
+
+def test_record_packing_roundtrip():
+    from dgx_vllm_b200 import moe_ep
+    h = torch.randn(5, 32).bfloat16()
+    w = torch.rand(5, 3)
+    ids = torch.randint(0, 8, (5, 3), dtype=torch.int32)
+    rec = moe_ep.pack_records(h, w, ids)
+    h2, w2, i2 = moe_ep.unpack_records(rec, 32, 3, torch.bfloat16)
+    assert torch.equal(h, h2) and torch.equal(w, w2) and torch.equal(ids, i2)
+    m = moe_ep.expert_map_for_rank(8, 2, 1, "cpu")
+    assert m.tolist() == [-1, -1, -1, -1, 0, 1, 2, 3]
+
+
+_WORKER = r'''
+import os, sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import numpy as np, torch, torch.distributed as dist
+import oracle
+from util import oracle_quantize_fn
+from dgx_vllm_b200 import synth
+from dgx_vllm_b200.moe_ep import ExpertParallelMoE
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+E, H, I, B, topk = 8, 64, 32, 3, 2
+keys = ("comp_T", "meta_T", "scale_T", "g_scales")
+full13 = synth.make_sparse_experts(E, 2 * I, H, 1, "cpu", oracle_quantize_fn)
+full2 = synth.make_sparse_experts(E, H, I, 2, "cpu", oracle_quantize_fn)
+per = E // world
+loc13 = {k: full13[k][rank * per:(rank + 1) * per] for k in keys}
+loc2 = {k: full2[k][rank * per:(rank + 1) * per] for k in keys}
+def local_fn(hidden, tw, ids, emap):       # CPU stand-in for the CUDA op: the oracle
+    out = oracle.fused_sparse_moe(hidden.float().numpy(), tw.numpy(), ids.numpy(), emap.numpy(),
+                                  tuple(loc13[k].numpy() for k in keys), tuple(loc2[k].numpy() for k in keys), I,
+                                  round_fp16=False)
+    return torch.from_numpy(out).to(hidden.dtype)
+layer = ExpertParallelMoE(E, I, None, None, local_moe_fn=local_fn)
+tw, ids = synth.make_routing(B, E, topk, 10 + rank, "cpu")
+hidden = synth.make_hidden(B, H, 20 + rank, "cpu")
+out = layer.forward(hidden, tw, ids)
+ref = oracle.fused_sparse_moe(hidden.float().numpy(), tw.numpy(), ids.numpy(), None,
+                              tuple(full13[k].numpy() for k in keys), tuple(full2[k].numpy() for k in keys), I,
+                              round_fp16=False)
+err = float(np.max(np.abs(out.float().numpy() - ref)) / np.max(np.abs(ref)))
+assert err < 2e-2, err          # bf16 partial rows per owner rank
+print(f"rank {rank} ok err={err:.3e}")
+dist.destroy_process_group()
+'''
+
+
+def test_expert_parallel_dispatch_combine_gloo_world2(tmp_path):
+    script = tmp_path / "ep_worker.py"
+    script.write_text(_WORKER)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
