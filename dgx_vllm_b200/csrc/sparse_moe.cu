@@ -1,29 +1,37 @@
 // 2:4-sparse NVFP4 batched GEMV and the fused MoE decode layer for sm_100a.
 //
 // Replaces sparse_fp4_kernel/sparse_fp4_v7.cu of the reference with a different execution plan:
-//   * a one-block "plan" kernel groups the (token, expert) pairs by expert, so each expert's
-//     weights are streamed from HBM once per layer instead of once per pair;
-//   * a persistent GEMV kernel walks (expert, 128-column slab) work items.  Each thread owns 16
-//     output columns (one 16-byte load per weight row) and one of 32 K-slices; the K reduction is
-//     done in-kernel with warp shuffles plus one shared-memory pass, so no partial-sum tensor and
-//     no second reduction kernel exist;
-//   * E2M1 byte -> half2 and metadata byte -> byte-permute selector decoding go through two
-//     bank-replicated shared-memory tables, the 2:4 gather of the activation is one PRMT, and the
-//     products run as packed half2 FMAs with fp32 accumulation per 16-element scale block;
-//   * SiLU(gate)*up is fused into the gate_up epilogue and the router-weighted sum is one small
-//     deterministic kernel (no atomics).
+//   * a "plan" kernel groups the (token, expert) pairs by expert and cuts them into passes of at
+//     most four tokens, so an expert's weights are streamed from HBM once per layer (per pass)
+//     instead of once per pair;
+//   * a persistent GEMV kernel (one block per SM) walks (pass, column slab) work items.  A thread
+//     owns 16 output columns and one K-slice.  Its weight bytes (four compressed rows, two
+//     metadata rows, one scale row per 16 k) arrive through a private multi-stage cp.async ring in
+//     shared memory that keeps running across work-item boundaries, so HBM latency is hidden
+//     without holding prefetched data in registers;
+//   * E2M1 byte -> half2 and metadata byte -> byte-permute selector decoding are table look-ups in
+//     shared memory (32 copies per entry, one per bank: conflict free); the table index is built by
+//     a single PRMT that merges the byte with the lane's bank offset;
+//   * the 2:4 gather of the activation is one PRMT, products are packed half2 FMAs, and every
+//     16-element scale block is folded into an fp32 accumulator;
+//   * the K reduction is done in-kernel (warp shuffles, then one shared-memory pass), so there is
+//     no partial-sum tensor and no separate reduction kernel; SiLU(gate)*up is fused into the
+//     gate_up epilogue; the router-weighted sum is a small deterministic kernel (no atomics).
+#include <type_traits>
+
 #include "common.cuh"
+
+extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E);
 
 namespace b200fp4 {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kSlabCols = 128;   // output columns per work item
-constexpr int kKSlices = 32;     // K-slices per block (4 per warp)
 constexpr int kMaxTok = 4;       // tokens of one expert processed per pass over its weights
 constexpr int kPlanThreads = 1024;
 constexpr int kPlanMaxExperts = 4096;
+constexpr int kLutBytes = 256 * 256;   // 256 rows of [32 x comp entry | 32 x meta entry]
 
 // Where one projection's weights live.  Row r of the compressed tensor for expert e and column n:
 //   comp  + e*comp_e  + (r/2)*comp_pair + (r&1)*comp_odd + n
@@ -42,35 +50,47 @@ struct SparseWeights {
 };
 
 struct Plan {
-  int* n_unique;     // [1]
-  int* uniq_expert;  // [U]
-  int* uniq_start;   // [U+1]
-  int* pairs;        // [P]  pair indices grouped by expert
-  int* mapped;       // [P]  local expert id of each pair, or -1
+  int* hdr;        // [0] = number of unique experts, [1] = number of passes
+  int* pairs;      // [P]  pair indices grouped by expert
+  int* mapped;     // [P]  local expert id of each pair, or -1
+  int4* pass_rec;  // [passes][2]: {expert, n_tokens, pair0, pair1}, {pair2, pair3, -, -}
 };
 
 struct GemvArgs {
   SparseWeights w;
   Plan plan;
-  const void* A;  // [rows, K]; the row of pair p is p / a_div
+  const __half* A;  // [rows, K] fp16; the row of pair p is p / a_div
   int64_t lda;
   int a_div;
-  int a_bf16;
-  void* out;      // [P, N] (or [P, N/2] in SiLU mode), leading dimension ldo
+  void* out;        // [P, N] (or [P, N/2] in SiLU mode), leading dimension ldo
   int64_t ldo;
   int out_dtype;
   int N, K;
   int n_slabs;
-  int inter;      // SiLU mode: gate columns [0, inter), up columns [inter, 2*inter)
+  int inter;        // SiLU mode: gate columns [0, inter), up columns [inter, 2*inter)
 };
 
 // ------------------------------------------------------------------------------------------ plan
 
+// Block 0 builds the plan; the remaining blocks (if any) convert a bf16 activation matrix to fp16.
 __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
-                    Plan plan) {
+                    Plan plan, const __nv_bfloat16* __restrict__ conv_src, __half* __restrict__ conv_dst,
+                    int64_t conv_chunks) {
+  if (blockIdx.x > 0) {
+    const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
+    for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
+      const uint4 raw = reinterpret_cast<const uint4*>(conv_src)[i];
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      __half2 h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) h[k] = __float22half2_rn(__bfloat1622float2(b2[k]));
+      reinterpret_cast<uint4*>(conv_dst)[i] = *reinterpret_cast<uint4*>(h);
+    }
+    return;
+  }
   __shared__ int s_count[kPlanMaxExperts];
-  __shared__ int s_warp_a[32], s_warp_b[32];
+  __shared__ int s_warp[3][32];
   const int tid = threadIdx.x;
   for (int e = tid; e < E; e += kPlanThreads) s_count[e] = 0;
   __syncthreads();
@@ -82,71 +102,89 @@ __global__ void __launch_bounds__(kPlanThreads)
     if (e >= 0) atomicAdd(&s_count[e], 1);
   }
   __syncthreads();
-  // exclusive scan over experts of (count, count > 0); each thread owns a contiguous run
+  // exclusive scans over experts of (pairs, present, passes); each thread owns a contiguous run
   const int per = (E + kPlanThreads - 1) / kPlanThreads;
   const int e0 = tid * per;
-  int sum_c = 0, sum_f = 0;
+  int sum[3] = {0, 0, 0};
   for (int i = 0; i < per; ++i) {
-    int e = e0 + i;
+    const int e = e0 + i;
     if (e < E) {
-      sum_c += s_count[e];
-      sum_f += s_count[e] > 0;
+      const int c = s_count[e];
+      sum[0] += c;
+      sum[1] += c > 0;
+      sum[2] += (c + kMaxTok - 1) / kMaxTok;
     }
   }
-  int inc_c = sum_c, inc_f = sum_f;
+  int inc[3] = {sum[0], sum[1], sum[2]};
   const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    int a = __shfl_up_sync(0xffffffffu, inc_c, d);
-    int b = __shfl_up_sync(0xffffffffu, inc_f, d);
-    if (lane >= d) {
-      inc_c += a;
-      inc_f += b;
+  for (int d = 1; d < 32; d <<= 1)
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      const int v = __shfl_up_sync(0xffffffffu, inc[k], d);
+      if (lane >= d) inc[k] += v;
     }
-  }
-  if (lane == 31) {
-    s_warp_a[warp] = inc_c;
-    s_warp_b[warp] = inc_f;
-  }
+  if (lane == 31)
+#pragma unroll
+    for (int k = 0; k < 3; ++k) s_warp[k][warp] = inc[k];
   __syncthreads();
   if (warp == 0) {
-    int a = s_warp_a[lane], b = s_warp_b[lane];
+    int v[3] = {s_warp[0][lane], s_warp[1][lane], s_warp[2][lane]};
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      int x = __shfl_up_sync(0xffffffffu, a, d);
-      int y = __shfl_up_sync(0xffffffffu, b, d);
-      if (lane >= d) {
-        a += x;
-        b += y;
+    for (int d = 1; d < 32; d <<= 1)
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        const int x = __shfl_up_sync(0xffffffffu, v[k], d);
+        if (lane >= d) v[k] += x;
       }
-    }
-    s_warp_a[lane] = a;
-    s_warp_b[lane] = b;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) s_warp[k][lane] = v[k];
   }
   __syncthreads();
-  int base_c = inc_c - sum_c + (warp > 0 ? s_warp_a[warp - 1] : 0);
-  int base_f = inc_f - sum_f + (warp > 0 ? s_warp_b[warp - 1] : 0);
-  for (int i = 0; i < per; ++i) {
-    int e = e0 + i;
-    if (e < E) {
-      int c = s_count[e];
-      if (c > 0) {
-        plan.uniq_expert[base_f] = e;
-        plan.uniq_start[base_f] = base_c;
-        ++base_f;
+  int base[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) base[k] = inc[k] - sum[k] + (warp > 0 ? s_warp[k][warp - 1] : 0);
+  const int my_pair_base = base[0], my_pass_base = base[2];
+  {
+    int bc = base[0];
+    for (int i = 0; i < per; ++i) {
+      const int e = e0 + i;
+      if (e < E) {
+        const int c = s_count[e];
+        s_count[e] = bc;  // becomes the scatter cursor
+        bc += c;
       }
-      s_count[e] = base_c;  // becomes the scatter cursor
-      base_c += c;
     }
   }
   if (tid == kPlanThreads - 1) {
-    plan.n_unique[0] = base_f;
-    plan.uniq_start[base_f] = base_c;
+    plan.hdr[0] = base[1] + sum[1];
+    plan.hdr[1] = base[2] + sum[2];
   }
   __syncthreads();
   for (int p = tid; p < P; p += kPlanThreads) {
-    int e = plan.mapped[p];
+    const int e = plan.mapped[p];
     if (e >= 0) plan.pairs[atomicAdd(&s_count[e], 1)] = p;
+  }
+  __syncthreads();  // pairs[] (global) written by this block are visible to it after the barrier
+  // pass records of the experts this thread owns; after the scatter s_count[e] is the END of e's run
+  {
+    int start = my_pair_base, pass = my_pass_base;
+    for (int i = 0; i < per; ++i) {
+      const int e = e0 + i;
+      if (e < E) {
+        const int end = s_count[e];
+        for (int s0 = start; s0 < end; s0 += kMaxTok) {
+          const int nt = min(kMaxTok, end - s0);
+          int pr[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) pr[t] = t < nt ? plan.pairs[s0 + t] : 0;
+          plan.pass_rec[2 * pass] = make_int4(e, nt, pr[0], pr[1]);
+          plan.pass_rec[2 * pass + 1] = make_int4(pr[2], pr[3], 0, 0);
+          ++pass;
+        }
+        start = end;
+      }
+    }
   }
 }
 
@@ -159,9 +197,10 @@ __device__ __forceinline__ uint32_t e2m1_to_half_bits(uint32_t nib) {
   return h;
 }
 
-// table[b][lane]: 32 copies of every entry, one per bank, so that 32 lanes looking up 32 different
-// bytes never conflict.  Writes are rotated by the thread index for the same reason.
-__device__ __forceinline__ void fill_tables(uint32_t* lut_c, uint32_t* lut_m, int tid) {
+// Row b (256 bytes) of the table: words 0..31 hold 32 copies of the half2 pair decoded from the
+// compressed byte b, words 32..63 hold 32 copies of the two PRMT selectors decoded from the
+// metadata byte b.  A lane always reads word `lane` (or 32+lane), i.e. its own bank.
+__device__ __forceinline__ void fill_tables(uint32_t* lut, int tid) {
   for (int b = tid; b < 256; b += kThreads) {
     const uint32_t vc = e2m1_to_half_bits(b & 15) | (e2m1_to_half_bits(b >> 4) << 16);
     const uint32_t i0 = b & 3, i1 = (b >> 2) & 3, i2 = (b >> 4) & 3, i3 = (b >> 6) & 3;
@@ -170,152 +209,81 @@ __device__ __forceinline__ void fill_tables(uint32_t* lut_c, uint32_t* lut_m, in
     const uint32_t vm = s0 | (s1 << 16);
 #pragma unroll 4
     for (int i = 0; i < 32; ++i) {
-      const int l = (i + tid) & 31;
-      lut_c[b * 32 + l] = vc;
-      lut_m[b * 32 + l] = vm;
+      const int l = (i + tid) & 31;  // rotate so that the 32 threads of a warp hit 32 banks
+      lut[b * 64 + l] = vc;
+      lut[b * 64 + 32 + l] = vm;
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------ GEMV
 
-struct BlockLoads {
-  uint4 c[4];  // four compressed rows (16 k) x 16 columns
-  uint4 m[2];  // two metadata rows
-  uint4 s[2];  // scale row(s): s[1] is used only with one scale per 8 k
-};
-
-template <bool kScale8>
-__device__ __forceinline__ void load_block(BlockLoads& L, const uint8_t* comp, const uint8_t* meta,
-                                           const uint8_t* scale, const SparseWeights& w, int kb, bool ok) {
-  if (ok) {
-    const uint8_t* c0 = comp + (int64_t)(2 * kb) * w.comp_pair;
-    L.c[0] = ldg_stream_u4(c0);
-    L.c[1] = ldg_stream_u4(c0 + w.comp_odd);
-    L.c[2] = ldg_stream_u4(c0 + w.comp_pair);
-    L.c[3] = ldg_stream_u4(c0 + w.comp_pair + w.comp_odd);
-    const uint8_t* m0 = meta + (int64_t)(2 * kb) * w.meta_row;
-    L.m[0] = ldg_stream_u4(m0);
-    L.m[1] = ldg_stream_u4(m0 + w.meta_row);
-    if (kScale8) {
-      const uint8_t* s0 = scale + (int64_t)(2 * kb) * w.scale_row;
-      L.s[0] = ldg_stream_u4(s0);
-      L.s[1] = ldg_stream_u4(s0 + w.scale_row);
-    } else {
-      L.s[0] = ldg_stream_u4(scale + (int64_t)kb * w.scale_row);
-    }
-  } else {
-    L.c[0] = L.c[1] = L.c[2] = L.c[3] = L.m[0] = L.m[1] = L.s[0] = L.s[1] = make_uint4(0, 0, 0, 0);
-  }
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 __device__ __forceinline__ uint32_t word_of(const uint4& v, int q) {
   return q == 0 ? v.x : (q == 1 ? v.y : (q == 2 ? v.z : v.w));
 }
-
-// byte j of w, shifted left by 7 (the row pitch of the replicated tables), masked.
-template <int J>
-__device__ __forceinline__ uint32_t byte_shl7(uint32_t w, uint32_t mask) {
-  return (J == 0 ? (w << 7) : (w >> (8 * J - 7))) & mask;
-}
-
 __device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
+// One scale block (16 k) x 16 columns for T tokens.  v[] = 4 compressed rows, 2 metadata rows,
+// 1 (or 2) scale rows; a[t] = the 16 activations of token t as 8 half2.
 template <int T, bool kScale8>
-__device__ __forceinline__ void compute_block(const BlockLoads& L, const uint4 (&a)[T][2], const uint32_t* lut_c,
-                                              const uint32_t* lut_m, float (&acc)[T][16]) {
-  // lut_c / lut_m already include this lane's bank offset.
+__device__ __forceinline__ void compute_block(const uint4 (&v)[8], const uint4 (&a)[T][2], const unsigned char* lut,
+                                              uint32_t lane4, float (&acc)[T][16]) {
+  // PRMT selectors: (table row = byte j of the word) << 8 | lane*4
+  constexpr uint32_t kIdx[4] = {0x5504u, 0x5514u, 0x5524u, 0x5534u};
+  // PRMT selectors: bytes (j, j+1) of the scale word to the high bytes of two halves
+  constexpr uint32_t kSc[2] = {0x1404u, 0x3424u};
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
-    const uint32_t c0 = word_of(L.c[0], q), c1 = word_of(L.c[1], q), c2 = word_of(L.c[2], q), c3 = word_of(L.c[3], q);
-    const uint32_t m0 = word_of(L.m[0], q), m1 = word_of(L.m[1], q);
-    const uint32_t s0 = word_of(L.s[0], q), s1 = kScale8 ? word_of(L.s[1], q) : 0u;
+    const uint32_t c0 = word_of(v[0], q), c1 = word_of(v[1], q), c2 = word_of(v[2], q), c3 = word_of(v[3], q);
+    const uint32_t m0 = word_of(v[4], q), m1 = word_of(v[5], q);
+    const uint32_t s0 = word_of(v[6], q) & 0x7F7F7F7Fu;
+    const uint32_t s1 = kScale8 ? (word_of(v[7], q) & 0x7F7F7F7Fu) : 0u;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint32_t i0, i1, i2, i3, im0, im1, hs0, hs1 = 0;
-      // clang-format off
-      if (j == 0) { i0 = byte_shl7<0>(c0, 0x7F80u); i1 = byte_shl7<0>(c1, 0x7F80u); i2 = byte_shl7<0>(c2, 0x7F80u); i3 = byte_shl7<0>(c3, 0x7F80u);
-                    im0 = byte_shl7<0>(m0, 0x7F80u); im1 = byte_shl7<0>(m1, 0x7F80u); hs0 = byte_shl7<0>(s0, 0x3F80u); if (kScale8) hs1 = byte_shl7<0>(s1, 0x3F80u); }
-      if (j == 1) { i0 = byte_shl7<1>(c0, 0x7F80u); i1 = byte_shl7<1>(c1, 0x7F80u); i2 = byte_shl7<1>(c2, 0x7F80u); i3 = byte_shl7<1>(c3, 0x7F80u);
-                    im0 = byte_shl7<1>(m0, 0x7F80u); im1 = byte_shl7<1>(m1, 0x7F80u); hs0 = byte_shl7<1>(s0, 0x3F80u); if (kScale8) hs1 = byte_shl7<1>(s1, 0x3F80u); }
-      if (j == 2) { i0 = byte_shl7<2>(c0, 0x7F80u); i1 = byte_shl7<2>(c1, 0x7F80u); i2 = byte_shl7<2>(c2, 0x7F80u); i3 = byte_shl7<2>(c3, 0x7F80u);
-                    im0 = byte_shl7<2>(m0, 0x7F80u); im1 = byte_shl7<2>(m1, 0x7F80u); hs0 = byte_shl7<2>(s0, 0x3F80u); if (kScale8) hs1 = byte_shl7<2>(s1, 0x3F80u); }
-      if (j == 3) { i0 = byte_shl7<3>(c0, 0x7F80u); i1 = byte_shl7<3>(c1, 0x7F80u); i2 = byte_shl7<3>(c2, 0x7F80u); i3 = byte_shl7<3>(c3, 0x7F80u);
-                    im0 = byte_shl7<3>(m0, 0x7F80u); im1 = byte_shl7<3>(m1, 0x7F80u); hs0 = byte_shl7<3>(s0, 0x3F80u); if (kScale8) hs1 = byte_shl7<3>(s1, 0x3F80u); }
-      // clang-format on
-      const __half2 w0 = as_h2(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_c) + i0));
-      const __half2 w1 = as_h2(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_c) + i1));
-      const __half2 w2 = as_h2(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_c) + i2));
-      const __half2 w3 = as_h2(*reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_c) + i3));
-      const uint32_t sel01 = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_m) + im0);
-      const uint32_t sel23 = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(lut_m) + im1);
-      const uint32_t sel1 = sel01 >> 16, sel3 = sel23 >> 16;
-      // e4m3 bits placed in a half give scale * 2^-8; the 2^8 is folded into the final multiplier
-      const float sc0 = __half2float(__ushort_as_half((unsigned short)hs0));
-      const float sc1 = kScale8 ? __half2float(__ushort_as_half((unsigned short)hs1)) : 0.f;
-      const int col = q * 4 + j;
+    for (int jp = 0; jp < 2; ++jp) {
+      // e4m3 bits moved into a half give scale * 2^-8; the 2^8 is folded into the final multiplier
+      const float2 sc0 = __half22float2(as_h2(prmt(s0, 0u, kSc[jp]) >> 1));
+      float2 sc1 = make_float2(0.f, 0.f);
+      if (kScale8) sc1 = __half22float2(as_h2(prmt(s1, 0u, kSc[jp]) >> 1));
 #pragma unroll
-      for (int t = 0; t < T; ++t) {
-        __half2 p = __hmul2(w0, as_h2(prmt(a[t][0].x, a[t][0].y, sel01)));
-        p = __hfma2(w1, as_h2(prmt(a[t][0].z, a[t][0].w, sel1)), p);
-        if (kScale8) {
-          __half2 r = __hmul2(w2, as_h2(prmt(a[t][1].x, a[t][1].y, sel23)));
-          r = __hfma2(w3, as_h2(prmt(a[t][1].z, a[t][1].w, sel3)), r);
-          acc[t][col] = fmaf(__low2float(p) + __high2float(p), sc0, acc[t][col]);
-          acc[t][col] = fmaf(__low2float(r) + __high2float(r), sc1, acc[t][col]);
-        } else {
-          p = __hfma2(w2, as_h2(prmt(a[t][1].x, a[t][1].y, sel23)), p);
-          p = __hfma2(w3, as_h2(prmt(a[t][1].z, a[t][1].w, sel3)), p);
-          acc[t][col] = fmaf(__low2float(p) + __high2float(p), sc0, acc[t][col]);
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = jp * 2 + jj;
+        const int col = q * 4 + j;
+        const __half2 w0 = as_h2(lds32(lut + prmt(c0, lane4, kIdx[j])));
+        const __half2 w1 = as_h2(lds32(lut + prmt(c1, lane4, kIdx[j])));
+        const __half2 w2 = as_h2(lds32(lut + prmt(c2, lane4, kIdx[j])));
+        const __half2 w3 = as_h2(lds32(lut + prmt(c3, lane4, kIdx[j])));
+        const uint32_t sel01 = lds32(lut + 128 + prmt(m0, lane4, kIdx[j]));
+        const uint32_t sel23 = lds32(lut + 128 + prmt(m1, lane4, kIdx[j]));
+        const uint32_t sel1 = sel01 >> 16, sel3 = sel23 >> 16;
+        const float f0 = jj == 0 ? sc0.x : sc0.y;
+        const float f1 = jj == 0 ? sc1.x : sc1.y;
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          __half2 p = __hmul2(w0, as_h2(prmt(a[t][0].x, a[t][0].y, sel01)));
+          p = __hfma2(w1, as_h2(prmt(a[t][0].z, a[t][0].w, sel1)), p);
+          if (kScale8) {
+            __half2 r = __hmul2(w2, as_h2(prmt(a[t][1].x, a[t][1].y, sel23)));
+            r = __hfma2(w3, as_h2(prmt(a[t][1].z, a[t][1].w, sel3)), r);
+            acc[t][col] = fmaf(__half2float(__hadd(__low2half(p), __high2half(p))), f0, acc[t][col]);
+            acc[t][col] = fmaf(__half2float(__hadd(__low2half(r), __high2half(r))), f1, acc[t][col]);
+          } else {
+            p = __hfma2(w2, as_h2(prmt(a[t][1].x, a[t][1].y, sel23)), p);
+            p = __hfma2(w3, as_h2(prmt(a[t][1].z, a[t][1].w, sel3)), p);
+            acc[t][col] = fmaf(__half2float(__hadd(__low2half(p), __high2half(p))), f0, acc[t][col]);
+          }
         }
       }
-    }
-  }
-}
-
-template <int T, bool kScale8>
-__device__ __forceinline__ void gemv_pass(const GemvArgs& g, const uint8_t* comp, const uint8_t* meta,
-                                          const uint8_t* scale, bool col_ok, int kslice, int cg, int ksub, int warp,
-                                          const __half* sA, const uint32_t* lut_c, const uint32_t* lut_m, float* red) {
-  const int KB = g.K >> 4;
-  float acc[T][16];
-#pragma unroll
-  for (int t = 0; t < T; ++t)
-#pragma unroll
-    for (int c = 0; c < 16; ++c) acc[t][c] = 0.f;
-
-  BlockLoads cur, nxt;
-  int kb = kslice;
-  load_block<kScale8>(cur, comp, meta, scale, g.w, kb, col_ok && kb < KB);
-  for (; kb < KB; kb += kKSlices) {
-    const int kn = kb + kKSlices;
-    load_block<kScale8>(nxt, comp, meta, scale, g.w, kn, col_ok && kn < KB);
-    uint4 a[T][2];
-#pragma unroll
-    for (int t = 0; t < T; ++t) {
-      const uint4* pa = reinterpret_cast<const uint4*>(sA + (size_t)t * g.K + (size_t)kb * 16);
-      a[t][0] = pa[0];
-      a[t][1] = pa[1];
-    }
-    compute_block<T, kScale8>(cur, a, lut_c, lut_m, acc);
-    cur = nxt;
-  }
-  // K reduction: the four K-slices of a warp through shuffles, the eight warps through shared memory
-#pragma unroll
-  for (int t = 0; t < T; ++t)
-#pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      float v = acc[t][c];
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      acc[t][c] = v;
-    }
-  if (ksub == 0) {
-#pragma unroll
-    for (int t = 0; t < T; ++t) {
-      float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * kMaxTok + t) * kSlabCols + cg * 16);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) dst[c] = make_float4(acc[t][4 * c], acc[t][4 * c + 1], acc[t][4 * c + 2], acc[t][4 * c + 3]);
     }
   }
 }
@@ -326,102 +294,213 @@ __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, flo
   else reinterpret_cast<float*>(out)[idx] = v;
 }
 
-template <bool kScale8, bool kSilu>
+struct Rec {
+  int e, nt;
+  int p0, p1, p2, p3;
+  __device__ __forceinline__ int pair(int t) const { return t == 0 ? p0 : (t == 1 ? p1 : (t == 2 ? p2 : p3)); }
+};
+__device__ __forceinline__ Rec load_rec(const int4* recs, int pass) {
+  const int4 x = recs[2 * pass], y = recs[2 * pass + 1];
+  Rec r;
+  r.e = x.x; r.nt = x.y; r.p0 = x.z; r.p1 = x.w; r.p2 = y.x; r.p3 = y.y;
+  return r;
+}
+__device__ __forceinline__ Rec empty_rec() {
+  Rec r;
+  r.e = -1; r.nt = 0; r.p0 = r.p1 = r.p2 = r.p3 = 0;
+  return r;
+}
+
+// CG      16-column groups per slab (8, 16 or 32): slab = 16*CG columns, 256/CG K-slices
+// S       cp.async ring stages (2 or 3); every thread must own at least S-1 scale blocks per item
+// kScale8 one scale per 8 k instead of per 16 k
+// kSilu   slab = CG*8 gate columns + the matching CG*8 up columns; epilogue writes SiLU(gate)*up
+template <int CG, int S, bool kScale8, bool kSilu>
 __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs g) {
+  constexpr int KS = kThreads / CG;
+  constexpr int SLAB = CG * 16;
+  constexpr int NV = kScale8 ? 8 : 7;
   extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* lut_c = reinterpret_cast<uint32_t*>(smem);
-  uint32_t* lut_m = lut_c + 256 * 32;
-  float* red = reinterpret_cast<float*>(lut_m + 256 * 32);            // [kWarps][kMaxTok][kSlabCols]
-  __half* sA = reinterpret_cast<__half*>(red + kWarps * kMaxTok * kSlabCols);  // [kMaxTok][K]
+  uint32_t* lut_w = reinterpret_cast<uint32_t*>(smem);
+  uint4* ring = reinterpret_cast<uint4*>(smem + kLutBytes);                      // [S][NV][256]
+  float* red = reinterpret_cast<float*>(ring + S * NV * kThreads);               // [kWarps][kMaxTok][SLAB]
+  __half* sA = reinterpret_cast<__half*>(red + kWarps * kMaxTok * SLAB);         // [2][kMaxTok][K]
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-  const int cg = lane & 7, ksub = lane >> 3;
-  const int kslice = warp * 4 + ksub;
-  fill_tables(lut_c, lut_m, tid);
-  const uint32_t* lut_c_lane = lut_c + lane;
-  const uint32_t* lut_m_lane = lut_m + lane;
+  const int cg = lane % CG, ksub = lane / CG;
+  const int kslice = warp * (32 / CG) + ksub;
+  const uint32_t lane4 = (uint32_t)lane * 4u;
+  const int K = g.K, KB = K >> 4;
+  const int nblk = (KB - kslice + KS - 1) / KS;   // scale blocks this thread owns in every item (>= S-1)
+  const int grid = gridDim.x;
+  fill_tables(lut_w, tid);
 
-  const int n_unique = g.plan.n_unique[0];
-  const int n_work = n_unique * g.n_slabs;
-  for (int work = blockIdx.x; work < n_work; work += gridDim.x) {
-    const int u = work / g.n_slabs, slab = work - u * g.n_slabs;
-    const int e = g.plan.uniq_expert[u];
-    const int p0 = g.plan.uniq_start[u];
-    const int np = g.plan.uniq_start[u + 1] - p0;
-    // column owned by this thread
-    int col0;
-    if (kSilu) col0 = (cg < 4) ? slab * 64 + cg * 16 : g.inter + slab * 64 + (cg - 4) * 16;
-    else col0 = slab * kSlabCols + cg * 16;
-    const bool col_ok = kSilu ? ((cg < 4 ? col0 : col0 - g.inter) < g.inter) : (col0 < g.N);
-    const uint8_t* comp = g.w.comp + (int64_t)e * g.w.comp_e + col0;
-    const uint8_t* meta = g.w.meta + (int64_t)e * g.w.meta_e + col0;
-    const uint8_t* scale = g.w.scale + (int64_t)e * g.w.scale_e + col0;
-    const float gmul = g.w.g[e] * 256.0f;
+  const int n_items = g.plan.hdr[1] * g.n_slabs;
+  int item = blockIdx.x;
+  if (item >= n_items) return;
+  Rec rc = load_rec(g.plan.pass_rec, item / g.n_slabs);
+  Rec rn = (item + grid < n_items) ? load_rec(g.plan.pass_rec, (item + grid) / g.n_slabs) : empty_rec();
 
-    for (int tc = 0; tc < np; tc += kMaxTok) {
-      const int nt = min(kMaxTok, np - tc);
-      __syncthreads();  // tables ready (first pass) / previous pass done with sA and red
-      // stage the activations of this pass as fp16: sA[t][k]
-      const int chunks = g.K >> 3;
-      for (int i = tid; i < kMaxTok * chunks; i += kThreads) {
-        const int t = i / chunks, ch = i - t * chunks;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (t < nt) {
-          const int p = g.plan.pairs[p0 + tc + t];
-          const int64_t row = p / g.a_div;
-          if (g.a_bf16) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g.A) + row * g.lda + ch * 8);
-            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            __half2 h[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) h[k] = __float22half2_rn(__bfloat1622float2(b2[k]));
-            v = *reinterpret_cast<uint4*>(h);
-          } else {
-            v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(g.A) + row * g.lda + ch * 8);
-          }
-        }
-        *reinterpret_cast<uint4*>(sA + (size_t)t * g.K + ch * 8) = v;
+  // this thread's share of the activation rows of a pass -> sA[buf]
+  const int chunks = K >> 3;
+  auto issue_A = [&](const Rec& r, int buf) {
+    for (int i = tid; i < r.nt * chunks; i += kThreads) {
+      const int t = i / chunks, ch = i - t * chunks;
+      const int64_t row = r.pair(t) / g.a_div;
+      cp_async16(sA + ((size_t)(buf * kMaxTok + t) * K + ch * 8), g.A + row * g.lda + ch * 8);
+    }
+  };
+
+  // ---- weight fetch stream: runs S-1 blocks ahead of the compute and crosses item boundaries
+  int f_item = item, f_j = 0, f_slot = 0;
+  const uint8_t *f_comp = nullptr, *f_meta = nullptr, *f_scale = nullptr;
+  bool f_ok = false;
+  auto fetch_next = [&](const Rec& cur, const Rec& nxt) {
+    if (f_item < n_items) {
+      if (f_j == 0) {
+        const int e = (f_item == item) ? cur.e : nxt.e;
+        const int slab = f_item % g.n_slabs;
+        int col0;
+        if (kSilu) col0 = (cg < CG / 2) ? slab * (SLAB / 2) + cg * 16 : g.inter + slab * (SLAB / 2) + (cg - CG / 2) * 16;
+        else col0 = slab * SLAB + cg * 16;
+        f_ok = kSilu ? ((cg < CG / 2 ? col0 : col0 - g.inter) < g.inter) : (col0 < g.N);
+        f_comp = g.w.comp + (int64_t)e * g.w.comp_e + col0;
+        f_meta = g.w.meta + (int64_t)e * g.w.meta_e + col0;
+        f_scale = g.w.scale + (int64_t)e * g.w.scale_e + col0;
       }
-      __syncthreads();
-      if (nt == 1) gemv_pass<1, kScale8>(g, comp, meta, scale, col_ok, kslice, cg, ksub, warp, sA, lut_c_lane, lut_m_lane, red);
-      else if (nt == 2) gemv_pass<2, kScale8>(g, comp, meta, scale, col_ok, kslice, cg, ksub, warp, sA, lut_c_lane, lut_m_lane, red);
-      else gemv_pass<4, kScale8>(g, comp, meta, scale, col_ok, kslice, cg, ksub, warp, sA, lut_c_lane, lut_m_lane, red);
-      __syncthreads();
-      // epilogue: sum the eight warps, apply the expert's global scale, write
-      if (kSilu) {
-        for (int i = tid; i < nt * 64; i += kThreads) {
-          const int t = i >> 6, j = i & 63;
-          const int n = slab * 64 + j;
-          if (n < g.inter) {
-            float gate = 0.f, up = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-              gate += red[((size_t)w * kMaxTok + t) * kSlabCols + j];
-              up += red[((size_t)w * kMaxTok + t) * kSlabCols + 64 + j];
-            }
-            gate *= gmul;
-            up *= gmul;
-            const float act = gate / (1.0f + __expf(-gate)) * up;
-            const int p = g.plan.pairs[p0 + tc + t];
-            store_out(g.out, g.out_dtype, (int64_t)p * g.ldo + n, act);
-          }
+      if (f_ok) {
+        const int kb = kslice + KS * f_j;
+        uint4* dst = ring + (size_t)f_slot * NV * kThreads + tid;
+        const uint8_t* c0 = f_comp + (int64_t)(2 * kb) * g.w.comp_pair;
+        cp_async16(dst, c0);
+        cp_async16(dst + kThreads, c0 + g.w.comp_odd);
+        cp_async16(dst + 2 * kThreads, c0 + g.w.comp_pair);
+        cp_async16(dst + 3 * kThreads, c0 + g.w.comp_pair + g.w.comp_odd);
+        const uint8_t* m0 = f_meta + (int64_t)(2 * kb) * g.w.meta_row;
+        cp_async16(dst + 4 * kThreads, m0);
+        cp_async16(dst + 5 * kThreads, m0 + g.w.meta_row);
+        if (kScale8) {
+          const uint8_t* s0 = f_scale + (int64_t)(2 * kb) * g.w.scale_row;
+          cp_async16(dst + 6 * kThreads, s0);
+          cp_async16(dst + 7 * kThreads, s0 + g.w.scale_row);
+        } else {
+          cp_async16(dst + 6 * kThreads, f_scale + (int64_t)kb * g.w.scale_row);
         }
-      } else {
-        for (int i = tid; i < nt * kSlabCols; i += kThreads) {
-          const int t = i >> 7, j = i & 127;
-          const int n = slab * kSlabCols + j;
-          if (n < g.N) {
-            float v = 0.f;
+      }
+      if (++f_j == nblk) {
+        f_j = 0;
+        f_item += grid;
+      }
+    }
+    cp_async_commit();
+    f_slot = (f_slot + 1 == S) ? 0 : f_slot + 1;
+  };
+
+  // prologue: activations of the first item, then S-1 weight blocks
+  issue_A(rc, 0);
+  cp_async_commit();
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) v += red[((size_t)w * kMaxTok + t) * kSlabCols + j];
-            const int p = g.plan.pairs[p0 + tc + t];
-            store_out(g.out, g.out_dtype, (int64_t)p * g.ldo + n, v * gmul);
+  for (int s = 0; s < S - 1; ++s) fetch_next(rc, rn);
+
+  int c_slot = 0, abuf = 0;
+  for (; item < n_items; item += grid) {
+    const int slab = item % g.n_slabs;
+    // record of the item after next; activations of the next item ride on the next weight group
+    Rec rnn = (item + 2 * grid < n_items) ? load_rec(g.plan.pass_rec, (item + 2 * grid) / g.n_slabs) : empty_rec();
+    const float gmul = g.w.g[rc.e] * 256.0f;
+    cp_async_wait<S - 2>();   // oldest group: first weight block of this item and (older) its activations
+    __syncthreads();          // sA[abuf] complete for all threads; red and sA[abuf^1] free
+    issue_A(rn, abuf ^ 1);
+
+    float accs[kMaxTok][16];
+    auto run = [&](auto tconst) {
+      constexpr int T = decltype(tconst)::value;
+      float acc[T][16];
+#pragma unroll
+      for (int t = 0; t < T; ++t)
+#pragma unroll
+        for (int c = 0; c < 16; ++c) acc[t][c] = 0.f;
+      for (int j = 0; j < nblk; ++j) {
+        cp_async_wait<S - 2>();
+        uint4 v[8];
+        const uint4* src = ring + (size_t)c_slot * NV * kThreads + tid;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] = src[i * kThreads];
+        if (!kScale8) v[7] = make_uint4(0, 0, 0, 0);
+        fetch_next(rc, rn);
+        const int kb = kslice + KS * j;
+        uint4 a[T][2];
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          const uint4* pa = reinterpret_cast<const uint4*>(sA + ((size_t)(abuf * kMaxTok + t) * K + (size_t)kb * 16));
+          a[t][0] = pa[0];
+          a[t][1] = pa[1];
+        }
+        compute_block<T, kScale8>(v, a, smem, lane4, acc);
+        c_slot = (c_slot + 1 == S) ? 0 : c_slot + 1;
+      }
+      // K reduction: the K-slices of a warp through shuffles, then the warps through shared memory
+#pragma unroll
+      for (int t = 0; t < T; ++t)
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float x = acc[t][c];
+#pragma unroll
+          for (int d = CG; d < 32; d <<= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+          accs[t][c] = x;
+        }
+      if (ksub == 0) {
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * kMaxTok + t) * SLAB + cg * 16);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            dst[c] = make_float4(accs[t][4 * c], accs[t][4 * c + 1], accs[t][4 * c + 2], accs[t][4 * c + 3]);
+        }
+      }
+    };
+    if (rc.nt == 1) run(std::integral_constant<int, 1>{});
+    else if (rc.nt == 2) run(std::integral_constant<int, 2>{});
+    else if (rc.nt == 3) run(std::integral_constant<int, 3>{});
+    else run(std::integral_constant<int, 4>{});
+    __syncthreads();
+    // epilogue: sum the warps, apply the expert's global scale, write
+    if (kSilu) {
+      constexpr int HALF = SLAB / 2;
+      for (int i = tid; i < rc.nt * HALF; i += kThreads) {
+        const int t = i / HALF, j = i - t * HALF;
+        const int n = slab * HALF + j;
+        if (n < g.inter) {
+          float gate = 0.f, up = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            gate += red[((size_t)w * kMaxTok + t) * SLAB + j];
+            up += red[((size_t)w * kMaxTok + t) * SLAB + HALF + j];
           }
+          gate *= gmul;
+          up *= gmul;
+          const float act = gate / (1.0f + __expf(-gate)) * up;
+          store_out(g.out, g.out_dtype, (int64_t)rc.pair(t) * g.ldo + n, act);
+        }
+      }
+    } else {
+      for (int i = tid; i < rc.nt * SLAB; i += kThreads) {
+        const int t = i / SLAB, j = i - t * SLAB;
+        const int n = slab * SLAB + j;
+        if (n < g.N) {
+          float x = 0.f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) x += red[((size_t)w * kMaxTok + t) * SLAB + j];
+          store_out(g.out, g.out_dtype, (int64_t)rc.pair(t) * g.ldo + n, x * gmul);
         }
       }
     }
+    rc = rn;
+    rn = rnn;
+    abuf ^= 1;
   }
+  cp_async_wait<0>();
 }
 
 // Rows of pairs whose expert is not local are never touched by the GEMV; this writes zeros there.
@@ -506,53 +585,86 @@ cudaEvent_t g_prof_events[3] = {nullptr, nullptr, nullptr};
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+int64_t max_passes(int64_t P, int64_t E) { return (P < E ? P : E) + P / kMaxTok + 1; }
+
+// plan layout: hdr[4] | pairs[P] | mapped[P] | (16-byte aligned) pass_rec[max_passes][2] int4
 size_t plan_bytes(int64_t P, int64_t E) {
-  const int64_t U = P < E ? P : E;
-  return align_up(sizeof(int) * (size_t)(4 + U + (U + 1) + 2 * P), 256);
+  return align_up(sizeof(int) * (size_t)(4 + 2 * P), 16) + (size_t)max_passes(P, E) * 2 * sizeof(int4);
 }
 
 Plan carve_plan(void* ws, int64_t P, int64_t E) {
-  const int64_t U = P < E ? P : E;
+  (void)E;
   int* base = reinterpret_cast<int*>(ws);
   Plan pl;
-  pl.n_unique = base;
-  pl.uniq_expert = base + 4;
-  pl.uniq_start = pl.uniq_expert + U;
-  pl.pairs = pl.uniq_start + (U + 1);
+  pl.hdr = base;
+  pl.pairs = base + 4;
   pl.mapped = pl.pairs + P;
+  pl.pass_rec = reinterpret_cast<int4*>(reinterpret_cast<unsigned char*>(ws) + align_up(sizeof(int) * (size_t)(4 + 2 * P), 16));
   return pl;
 }
 
-size_t gemv_smem_bytes(int K) {
-  return (size_t)2 * 256 * 32 * 4 + (size_t)kWarps * kMaxTok * kSlabCols * 4 + (size_t)kMaxTok * K * 2;
+struct GemvCfg {
+  int cg, stages;
+  size_t smem;
+  bool ok;
+};
+
+GemvCfg pick_cfg(int64_t K, bool scale8) {
+  GemvCfg c = {0, 0, 0, false};
+  const int64_t KB = K / 16;
+  c.cg = KB >= 96 ? 8 : (KB >= 16 ? 16 : 32);
+  const int64_t KS = kThreads / c.cg;
+  const int64_t min_blocks = KB / KS;
+  if (min_blocks < 1) return c;
+  const int nv = scale8 ? 8 : 7;
+  for (int s = (c.cg == 32 ? 2 : 4); s >= 2; --s) {
+    if (min_blocks < s - 1) continue;
+    const size_t smem = (size_t)kLutBytes + (size_t)s * nv * kThreads * 16 +
+                        (size_t)kWarps * kMaxTok * c.cg * 16 * 4 + (size_t)2 * kMaxTok * K * 2;
+    if (smem <= 227 * 1024) {
+      c.stages = s;
+      c.smem = smem;
+      c.ok = true;
+      return c;
+    }
+  }
+  return c;
 }
 
-template <bool kScale8, bool kSilu>
-int launch_gemv(const GemvArgs& g, int64_t P, int64_t E, cudaStream_t st) {
+template <int CG, int S, bool kScale8, bool kSilu>
+int launch_gemv_t(const GemvArgs& g, int64_t grid, size_t smem, cudaStream_t st) {
   static bool attr_set[64] = {false};
-  const size_t smem = gemv_smem_bytes(g.K);
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(sparse_gemv_kernel<kScale8, kSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             200 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(sparse_gemv_kernel<CG, S, kScale8, kSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
     attr_set[dev] = true;
   }
-  const int64_t U = P < E ? P : E;
-  int64_t grid = U * g.n_slabs;
-  const int64_t cap = (int64_t)sm_count();
-  if (grid > cap) grid = cap;
-  if (grid < 1) grid = 1;
-  sparse_gemv_kernel<kScale8, kSilu><<<(unsigned)grid, kThreads, smem, st>>>(g);
+  sparse_gemv_kernel<CG, S, kScale8, kSilu><<<(unsigned)grid, kThreads, smem, st>>>(g);
   return B200FP4_STATUS_SUCCESS;
 }
 
+template <bool kScale8, bool kSilu>
+int launch_gemv(const GemvArgs& g, const GemvCfg& c, int64_t grid, cudaStream_t st) {
+  if (c.cg == 32) return launch_gemv_t<32, 2, kScale8, kSilu>(g, grid, c.smem, st);
+  if (c.cg == 8) {
+    if (c.stages == 4) return launch_gemv_t<8, 4, kScale8, kSilu>(g, grid, c.smem, st);
+    if (c.stages == 3) return launch_gemv_t<8, 3, kScale8, kSilu>(g, grid, c.smem, st);
+    return launch_gemv_t<8, 2, kScale8, kSilu>(g, grid, c.smem, st);
+  }
+  if (c.stages == 4) return launch_gemv_t<16, 4, kScale8, kSilu>(g, grid, c.smem, st);
+  if (c.stages == 3) return launch_gemv_t<16, 3, kScale8, kSilu>(g, grid, c.smem, st);
+  return launch_gemv_t<16, 2, kScale8, kSilu>(g, grid, c.smem, st);
+}
+
 bool vector_ok(int64_t N, int64_t K, int64_t G, const SparseWeights& w, const void* A, int64_t lda) {
-  if (N % 16 != 0 || K % 16 != 0 || K > 8192) return false;
+  if (N % 16 != 0 || K % 16 != 0) return false;
   if (G != K / 16 && G != K / 8) return false;
+  if (!pick_cfg(K, G == K / 8).ok) return false;
   if (!aligned(w.comp, 16) || !aligned(w.meta, 16) || !aligned(w.scale, 16) || !aligned(A, 16)) return false;
   if ((w.comp_e | w.comp_pair | w.comp_odd | w.meta_e | w.meta_row | w.scale_e | w.scale_row) % 16 != 0) return false;
   if (lda % 8 != 0) return false;
@@ -571,17 +683,31 @@ int check_common(const void* A, int a_dtype, const void* out, int out_dtype, int
   return B200FP4_STATUS_SUCCESS;
 }
 
-// Runs one projection for P pairs with a plan already in `plan`.
-int run_projection(const SparseWeights& w, const Plan& plan, const void* A, int a_bf16, int64_t lda, int a_div,
-                   void* out, int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E,
-                   int inter_silu, cudaStream_t st) {
+// Plan + (for bf16 activations) conversion to fp16 in one launch.
+void launch_plan(const int32_t* ids, int64_t P, const int32_t* expert_map, int64_t global_E, int64_t E,
+                 const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_elems, cudaStream_t st) {
+  int64_t chunks = 0;
+  unsigned blocks = 1;
+  if (a_bf16 != nullptr) {
+    chunks = a_elems / 8;
+    int64_t nb = (chunks + kPlanThreads - 1) / kPlanThreads;
+    if (nb > 2 * (int64_t)sm_count()) nb = 2 * (int64_t)sm_count();
+    blocks += (unsigned)(nb < 1 ? 1 : nb);
+  }
+  moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan,
+                                                   reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks);
+}
+
+// Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
+int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
+                   int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int inter_silu,
+                   cudaStream_t st) {
   GemvArgs g;
   g.w = w;
   g.plan = plan;
   g.A = A;
   g.lda = lda;
   g.a_div = a_div;
-  g.a_bf16 = a_bf16;
   g.out = out;
   g.ldo = ldo;
   g.out_dtype = out_dtype;
@@ -589,12 +715,15 @@ int run_projection(const SparseWeights& w, const Plan& plan, const void* A, int 
   g.K = (int)K;
   g.inter = inter_silu;
   const bool s8 = (G == K / 8);
-  if (inter_silu > 0) {
-    g.n_slabs = (inter_silu + 63) / 64;
-    return s8 ? launch_gemv<true, true>(g, P, E, st) : launch_gemv<false, true>(g, P, E, st);
-  }
-  g.n_slabs = (int)((N + kSlabCols - 1) / kSlabCols);
-  return s8 ? launch_gemv<true, false>(g, P, E, st) : launch_gemv<false, false>(g, P, E, st);
+  const GemvCfg c = pick_cfg(K, s8);
+  if (!c.ok) return B200FP4_STATUS_NOT_SUPPORTED;
+  const int slab = c.cg * 16;
+  g.n_slabs = inter_silu > 0 ? (inter_silu + slab / 2 - 1) / (slab / 2) : (int)((N + slab - 1) / slab);
+  int64_t grid = max_passes(P, E) * g.n_slabs;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  if (grid < 1) grid = 1;
+  if (inter_silu > 0) return s8 ? launch_gemv<true, true>(g, c, grid, st) : launch_gemv<false, true>(g, c, grid, st);
+  return s8 ? launch_gemv<true, false>(g, c, grid, st) : launch_gemv<false, false>(g, c, grid, st);
 }
 
 int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, const int32_t* expert_ids, void* out,
@@ -607,11 +736,14 @@ int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, con
   cudaStream_t st = (cudaStream_t)stream;
   const int a_bf16 = a_dtype == B200FP4_DTYPE_BF16;
   if (mode == 0 && E <= kPlanMaxExperts && vector_ok(N, K, G, w, A, K)) {
-    if (!workspace || ws_bytes < plan_bytes(P, E) || !aligned(workspace, 16)) return B200FP4_STATUS_ALLOC_FAILED;
+    if (!workspace || ws_bytes < b200fp4_sparse_workspace_bytes(P, K, E) || !aligned(workspace, 16))
+      return B200FP4_STATUS_ALLOC_FAILED;
     Plan plan = carve_plan(workspace, P, E);
-    moe_plan_kernel<<<1, kPlanThreads, 0, st>>>(expert_ids, (int)P, nullptr, 0, (int)E, plan);
+    __half* a16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + align_up(plan_bytes(P, E), 256));
+    launch_plan(expert_ids, P, nullptr, 0, E, plan, a_bf16 ? A : nullptr, a16, P * K, st);
     zero_unmapped_rows_kernel<<<(unsigned)P, 128, 0, st>>>(plan.mapped, (int)P, out, out_dtype, N, (int)N);
-    rc = run_projection(w, plan, A, a_bf16, K, 1, out, out_dtype, N, P, N, K, G, E, 0, st);
+    rc = run_projection(w, plan, a_bf16 ? a16 : reinterpret_cast<const __half*>(A), K, 1, out, out_dtype, N, P, N, K,
+                        G, E, 0, st);
     if (rc != B200FP4_STATUS_SUCCESS) return rc;
     return finish_launch(3);
   }
@@ -626,9 +758,9 @@ int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, con
 
 using namespace b200fp4;
 
-extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t E) {
-  if (P < 0 || E < 0) return 0;
-  return plan_bytes(P, E);
+extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E) {
+  if (P < 0 || E < 0 || K < 0) return 0;
+  return align_up(plan_bytes(P, E), 256) + align_up((size_t)P * K * sizeof(__half), 256);
 }
 
 extern "C" int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B_comp_T, const uint8_t* Meta_T_pk,
@@ -702,7 +834,8 @@ extern "C" void b200fp4_fused_moe_profile_events(void* before_gate_up, void* aft
 extern "C" size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
   const int64_t P = M * topk;
-  return plan_bytes(P, E) + align_up((size_t)P * I * sizeof(__half), 256) + align_up((size_t)P * H * sizeof(float), 256);
+  return align_up(plan_bytes(P, E), 256) + align_up((size_t)M * H * sizeof(__half), 256) +
+         align_up((size_t)P * I * sizeof(__half), 256) + align_up((size_t)P * H * sizeof(float), 256);
 }
 
 extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const float* topk_weights,
@@ -740,16 +873,21 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   Plan plan = carve_plan(ws, P, E);
-  __half* act = reinterpret_cast<__half*>(ws + plan_bytes(P, E));
-  float* down = reinterpret_cast<float*>(ws + plan_bytes(P, E) + align_up((size_t)P * I * sizeof(__half), 256));
+  size_t off = align_up(plan_bytes(P, E), 256);
+  __half* h16 = reinterpret_cast<__half*>(ws + off);
+  off += align_up((size_t)M * H * sizeof(__half), 256);
+  __half* act = reinterpret_cast<__half*>(ws + off);
+  off += align_up((size_t)P * I * sizeof(__half), 256);
+  float* down = reinterpret_cast<float*>(ws + off);
+  const bool bf = h_dtype == B200FP4_DTYPE_BF16;
 
-  moe_plan_kernel<<<1, kPlanThreads, 0, st>>>(topk_ids, (int)P, expert_map, (int)global_E, (int)E, plan);
+  launch_plan(topk_ids, P, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M * H, st);
   if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
-  rc = run_projection(w13, plan, hidden, h_dtype == B200FP4_DTYPE_BF16, H, (int)topk, act, B200FP4_DTYPE_F16, I, P,
-                      2 * I, H, G13, E, (int)I, st);
+  rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), H, (int)topk, act,
+                      B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
-  rc = run_projection(w2, plan, act, 0, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, st);
+  rc = run_projection(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);

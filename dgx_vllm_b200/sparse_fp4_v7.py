@@ -62,7 +62,7 @@ def batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, *,
     require(ids.numel() == P, "expert_ids must have one entry per row of A")
     out = torch.empty((P, N), dtype=_out_dtype(A, out_dtype), device=dev)
     L = _lib.lib()
-    nws = L.b200fp4_sparse_workspace_bytes(P, E)
+    nws = L.b200fp4_sparse_workspace_bytes(P, K, E)
     ws = workspace(dev, nws)
     with torch.cuda.device(dev):
         _lib.check(L.b200fp4_sparse_gemv(ptr(A), dtype_code(A.dtype), ptr(B_comp_T), ptr(Meta_T_pk), ptr(scales_T),
@@ -109,7 +109,7 @@ def batched_sparse_packed_v7(A, B_packed_T, g_scales, expert_ids, orig_K, *, out
     require(ids.numel() == P, "expert_ids must have one entry per row of A")
     out = torch.empty((P, N), dtype=_out_dtype(A, out_dtype), device=dev)
     L = _lib.lib()
-    ws = workspace(dev, L.b200fp4_sparse_workspace_bytes(P, E))
+    ws = workspace(dev, L.b200fp4_sparse_workspace_bytes(P, K, E))
     with torch.cuda.device(dev):
         _lib.check(L.b200fp4_sparse_packed_gemv(ptr(A), dtype_code(A.dtype), ptr(B_packed_T), ptr(g_scales), ptr(ids),
                                                 ptr(out), dtype_code(out.dtype), P, N, K, E, ptr(ws), ws.numel(),

@@ -104,10 +104,10 @@ B200FP4_API int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M,
  *   expert_ids [P] i32; ids outside [0, E) produce a zero row (the reference indexes out of
  *              bounds there)
  *   out        [P, N] (out_dtype f16 or bf16)
- *   workspace  b200fp4_sparse_workspace_bytes(P, E) bytes of scratch, 256-byte aligned
+ *   workspace  b200fp4_sparse_workspace_bytes(P, K, E) bytes of scratch, 256-byte aligned
  * N % 16 == 0 selects the vectorised kernel; other N fall back to a scalar kernel.
  * ------------------------------------------------------------------------------------------- */
-B200FP4_API size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t E);
+B200FP4_API size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E);
 
 /* batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids),
  * sparse_fp4_v7.cu:374-406.  B_comp_T [E, K/4, N], Meta_T_pk [E, K/8, N]. */

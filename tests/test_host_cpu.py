@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     assert L.b200fp4_version() >= 100
     assert b"success" in L.b200fp4_get_error_string(0)
     assert L.b200fp4_sf_swizzled_bytes(200, 12) == oracle.sf_swizzled_bytes(200, 12)
-    assert L.b200fp4_sparse_workspace_bytes(320, 512) > 0
+    assert L.b200fp4_sparse_workspace_bytes(320, 2048, 512) > 0
 
 
 def test_no_cpu_fallback():
