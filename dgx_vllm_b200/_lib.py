@@ -27,6 +27,8 @@ SIGNATURES = {
     "b200fp4_sf_swizzled_bytes": (_sz, [_i64, _i64]),
     "b200fp4_quantize": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "b200fp4_experts_quantize": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "b200fp4_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "b200fp4_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_sparse_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "b200fp4_sparse_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_dense_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),

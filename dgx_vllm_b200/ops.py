@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._torch_util import dtype_code, ptr, require, require_cuda, stream_ptr
+from ._torch_util import dtype_code, ptr, require, require_cuda, stream_ptr, workspace
 
 
 def scaled_fp4_quant(input: torch.Tensor, input_global_scale: torch.Tensor, is_sf_swizzled_layout: bool = True):
@@ -33,3 +33,47 @@ def scaled_fp4_quant(input: torch.Tensor, input_global_scale: torch.Tensor, is_s
                                       ptr(input_global_scale), ptr(codes), ptr(sf), 1 if is_sf_swizzled_layout else 0,
                                       stream_ptr(dev)), "scaled_fp4_quant")
     return codes, sf.view(torch.float8_e4m3fn)
+
+
+def cutlass_scaled_fp4_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch.Tensor, block_scale_b: torch.Tensor,
+                          alpha: torch.Tensor, out_dtype: torch.dtype, *, out: torch.Tensor | None = None,
+                          tile_n: int = 0) -> torch.Tensor:
+    """out[M,N] = alpha * (a . block_scale_a)(b . block_scale_b)^T on the tcgen05 tensor cores.
+
+    Mirrors cutlass_scaled_fp4_mm (vllm/_custom_ops.py:741-753): a [M,K/2] and b [N,K/2] packed E2M1
+    bytes, block scales in the swizzled 128x4 layout as produced by scaled_fp4_quant, alpha a
+    one-element f32 CUDA tensor, out_dtype bf16 or f16.  Pass `out` to write in place like the raw
+    torch.ops._C op does."""
+    dev = require_cuda(a, b, block_scale_a, block_scale_b, alpha)
+    require(a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], "a [M,K/2] and b [N,K/2] must share K")
+    require(a.dtype == torch.uint8 and b.dtype == torch.uint8, "a and b must be uint8 (packed E2M1)")
+    require(a.is_contiguous() and b.is_contiguous(), "a and b must be contiguous")
+    M, K2 = a.shape
+    N = b.shape[0]
+    K = K2 * 2
+    require(K % 64 == 0, "K must be a multiple of 64")
+    L = _lib.lib()
+    need_a, need_b = L.b200fp4_sf_swizzled_bytes(M, K // 16), L.b200fp4_sf_swizzled_bytes(N, K // 16)
+    for t, need, name in ((block_scale_a, need_a, "block_scale_a"), (block_scale_b, need_b, "block_scale_b")):
+        require(t.is_contiguous() and t.element_size() * t.numel() >= need,
+                f"{name} must be the swizzled scale tensor of at least {need} bytes")
+    require(alpha.dtype == torch.float32 and alpha.numel() == 1, "alpha must be one f32")
+    require(out_dtype in (torch.bfloat16, torch.float16), "out_dtype must be bfloat16 or float16")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    else:
+        require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N) and out.is_contiguous(),
+                "out must be a contiguous [M,N] CUDA tensor of out_dtype")
+    ws = workspace(dev, L.b200fp4_gemm_workspace_bytes(M, N, K))
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_gemm_nvfp4(ptr(a), ptr(b), ptr(block_scale_a), ptr(block_scale_b), ptr(alpha), ptr(out),
+                                        dtype_code(out_dtype), M, N, K, tile_n, ptr(ws), ws.numel(), stream_ptr(dev)),
+                   "cutlass_scaled_fp4_mm")
+    return out
+
+
+def last_gemm_status(device=None) -> int:
+    """Status word of the most recent GEMM on the current stream of `device` (0 = ok).  Synchronises."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.synchronize(dev)
+    return int(workspace(dev, 256)[:4].view(torch.int32).item())

@@ -94,6 +94,30 @@ B200FP4_API int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M,
                                          void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Part 2 -- dense block-scaled NVFP4 GEMM:  out[M,N] = alpha * (a . sfa)(b . sfb)^T.
+ * Replaces cudaFP4GemmEx (declared, never defined) of cutlass_nvfp4/cuda_fp4_gemm.h:94-105 and the
+ * software kernel launch_nvfp4_gemm (cutlass_nvfp4/nvfp4_gemm_kernel.cuh:350-386), with the
+ * argument convention of the op vLLM serves with, cutlass_scaled_fp4_mm(out, a, b, block_scale_a,
+ * block_scale_b, alpha) (vllm/_custom_ops.py:741-753), which the reference enables at
+ * cmake_patch_gb10_nvfp4_v6_full_kernels.sh:50-64.
+ *
+ *   a_codes [M, K/2] u8, b_codes [N, K/2] u8 (K-major packed E2M1), K % 64 == 0
+ *   sfa, sfb  E4M3 block scales in the padded 128x4-tile swizzled layout
+ *             (b200fp4_sf_swizzled_bytes(rows, K/16) bytes each)
+ *   alpha     device pointer to one f32 (= 1 / (global_scale_a * global_scale_b))
+ *   out       [M, N] bf16 or f16
+ *   tile_n    0 = choose; 128 or 256 forces the CTA tile width
+ *   workspace b200fp4_gemm_workspace_bytes() bytes; its first int is a status word the kernel
+ *             leaves at 0 unless one of its bounded barrier waits expired (then nothing it wrote
+ *             may be trusted): read it after synchronising when diagnosing.
+ * ------------------------------------------------------------------------------------------- */
+B200FP4_API size_t b200fp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+B200FP4_API int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* sfa,
+                                   const void* sfb, const float* alpha, void* out, int out_dtype,
+                                   int64_t M, int64_t N, int64_t K, int tile_n, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Part 3 -- 2:4-sparse / dense NVFP4 batched GEMV for MoE decode.
  * Replace the pybind functions of sparse_fp4_kernel/sparse_fp4_v7.cu:744-749.
  *
