@@ -177,6 +177,63 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
+    """Secondary measurements reported next to the headline: dense NVFP4 GEMM (BASELINE configs[1]:
+    N=14336, K=4096, M in {128,1024,4096}, activation quantized on the fly) and the quantizer alone.
+    Each iteration is timed on its own with CUDA events after rewriting a 256 MiB buffer (cold L2)."""
+    import torch
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant, synth
+
+    def timed(fn, n):
+        ts = []
+        for _ in range(3):
+            fn()
+        for _ in range(n):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        return statistics.mean(ts)
+
+    N, K = 14336, 4096
+    gen = torch.Generator(device=dev).manual_seed(7)
+    w = (0.02 * torch.randn(N, K, generator=gen, device=dev)).to(torch.bfloat16)
+    gw = synth.global_scale_of(w)
+    wc, ws = scaled_fp4_quant(w, gw)
+    del w
+    parts = {}
+    fp4_nominal = 9000.0      # TFLOP/s, dense NVFP4 nominal (4 x 2.25 PF bf16); no measured FP4 peak is provided
+    for M in (128, 1024, 4096):
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+        gx = synth.global_scale_of(x)
+        alpha = (1.0 / (gx * gw)).to(torch.float32)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        xc, xs = scaled_fp4_quant(x, gx)
+        t_mm = timed(lambda: cutlass_scaled_fp4_mm(xc, wc, xs, ws, alpha, torch.bfloat16, out=out), steps)
+
+        def both():
+            c, s_ = scaled_fp4_quant(x, gx)
+            cutlass_scaled_fp4_mm(c, wc, s_, ws, alpha, torch.bfloat16, out=out)
+        t_all = timed(both, steps)
+        flops = 2.0 * M * N * K
+        byt = N * K * 0.5625 + M * K * 0.5625 + 2.0 * M * N
+        parts[f"dense_gemm_m{M}"] = {
+            "gemm_us": t_mm * 1e6, "quant_plus_gemm_us": t_all * 1e6, "tflops": flops / t_mm / 1e12,
+            "frac_of_nominal_fp4_peak": flops / t_mm / 1e12 / fp4_nominal,
+            "hbm_GBps": byt / t_mm / 1e9, "frac_of_measured_hbm": byt / t_mm / 1e9 / hbm_peak,
+            "bound": "hbm" if M < 316 else "tensor"}
+    for M in (4096, 16384):
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+        gx = synth.global_scale_of(x)
+        t_q = timed(lambda: scaled_fp4_quant(x, gx), steps)
+        byt = M * K * 2.5625
+        parts[f"quantizer_{M}x{K}"] = {"us": t_q * 1e6, "GBps": byt / t_q / 1e9, "frac_of_measured_hbm": byt / t_q / 1e9 / hbm_peak}
+    return parts
+
+
 def config_dict(args):
     return {"workload": "sparse 2:4 NVFP4 MoE GEMV decode layer (BASELINE configs[2])", "experts": E_TOTAL,
             "hidden": HIDDEN, "moe_intermediate": INTER, "topk": TOPK, "batch_per_gpu": args.batch,
@@ -194,6 +251,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parts", action="store_true", help="skip the dense GEMM / quantizer side measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -337,6 +395,10 @@ def main():
                 "data": "synthetic", "config": config_dict(args), "roofline": roofline,
                 "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                 "gpu_launches": launches, "clocks": clocks}
+        if world == 1 and not args.no_parts:
+            del w13, w2, layer
+            torch.cuda.empty_cache()
+            line["parts"] = bench_dense_parts(dev, flush, hbm_peak)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(B)
         print(json.dumps(line), flush=True)
