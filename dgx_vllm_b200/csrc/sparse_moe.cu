@@ -782,6 +782,67 @@ extern "C" int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B_
   return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, G, E, workspace, workspace_bytes, stream);
 }
 
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of b200fp4_sparse_gemv.
+//
+// Some hosts must not (or cannot) hand this library a workspace: plug-ins loaded into an inference
+// server whose memory pool has already claimed nearly all device memory (a late cudaMalloc fails or
+// fragments the pool), and latency-critical loops that ban allocator calls because cudaMalloc and
+// cudaFree synchronise the whole device.  For them the scratch of the GEMV (the pair plan and the
+// fp16 copy of bf16 activations) lives in a fixed array inside the library image instead.
+//
+// The array exists once per GPU that loads the library and stays resident until the process exits.
+// All calls on a GPU share it: it still holds the previous call's plan when the next call starts
+// (harmless -- the plan kernel rewrites every word the GEMV reads, so nothing has to be cleared), and
+// two calls that overlap on the GPU (different streams, or different host threads) would overwrite
+// each other's plan: serialise them.
+constexpr int64_t kStaticMaxPairs = 512;
+constexpr int64_t kStaticMaxK = 4096;
+constexpr int64_t kStaticMaxExperts = 4096;
+constexpr size_t static_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
+constexpr size_t kStaticPlanBytes =
+    static_align(sizeof(int) * (size_t)(4 + 2 * kStaticMaxPairs), 16) +
+    (size_t)(kStaticMaxPairs + kStaticMaxPairs / 4 + 1) * 2 * sizeof(int4);
+constexpr size_t kStaticScratchBytes =
+    static_align(kStaticPlanBytes, 256) + static_align((size_t)kStaticMaxPairs * kStaticMaxK * sizeof(__half), 256);
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the symbol's name is only
+// a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+static int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return B200FP4_STATUS_NOT_INITIALIZED;
+  }
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return B200FP4_STATUS_INTERNAL_ERROR;
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return B200FP4_STATUS_SUCCESS;
+}
+
+extern "C" int b200fp4_sparse_gemv_static(const void* A, int a_dtype, const uint8_t* B_comp_T, const uint8_t* Meta_T_pk,
+                                          const uint8_t* scales_T, const float* g_scales, const int32_t* expert_ids,
+                                          void* out, int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E,
+                                          void* stream) {
+  // sizes the fixed scratch cannot hold are refused before anything is enqueued
+  if (P > kStaticMaxPairs || K > kStaticMaxK || E > kStaticMaxExperts) return B200FP4_STATUS_NOT_SUPPORTED;
+  void* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);
+  if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  return b200fp4_sparse_gemv(A, a_dtype, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, out, out_dtype, P, N, K, G,
+                             E, scratch, kStaticScratchBytes, stream);
+}
+
 extern "C" int b200fp4_dense_gemv(const void* A, int a_dtype, const uint8_t* B_dense_T, const uint8_t* scales_T,
                                   const float* g_scales, const int32_t* expert_ids, void* out, int out_dtype, int64_t P,
                                   int64_t N, int64_t K, int64_t G, int64_t E, void* workspace, size_t workspace_bytes,

@@ -141,6 +141,23 @@ B200FP4_API int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B
                                     int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G,
                                     int64_t E, void* workspace, size_t workspace_bytes, void* stream);
 
+/* b200fp4_sparse_gemv without a caller workspace.  No counterpart in the reference: it exists
+ * for hosts that cannot allocate device memory around the call -- e.g. a plug-in inside a serving
+ * process whose pool already owns the GPU's memory, or a loop that bans cudaMalloc/cudaFree because
+ * they synchronise the device.  The scratch is a fixed ~4.2 MB array inside the library (resident on
+ * every GPU that loads it, until exit), so the call is limited to P <= 512 pairs, K <= 4096 and
+ * E <= 4096; larger sizes return B200FP4_STATUS_NOT_SUPPORTED and enqueue nothing.  Same arguments,
+ * results and validation as b200fp4_sparse_gemv otherwise; it calls no allocator.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress): make
+ * that first call outside any stream capture.  All calls on a GPU share the array, which keeps the
+ * previous call's contents (nothing needs clearing: every word read is rewritten first); calls
+ * that overlap on the GPU race on it, so issue them on one stream or otherwise serialise them. */
+B200FP4_API int b200fp4_sparse_gemv_static(const void* A, int a_dtype, const uint8_t* B_comp_T,
+                                           const uint8_t* Meta_T_pk, const uint8_t* scales_T,
+                                           const float* g_scales, const int32_t* expert_ids,
+                                           void* out, int out_dtype, int64_t P, int64_t N, int64_t K,
+                                           int64_t G, int64_t E, void* stream);
+
 /* batched_dense_v7(A, B_dense_T, scales_T, g_scales, expert_ids), sparse_fp4_v7.cu:341-372.
  * B_dense_T [E, K/2, N]. */
 B200FP4_API int b200fp4_dense_gemv(const void* A, int a_dtype, const uint8_t* B_dense_T,
