@@ -42,7 +42,46 @@ struct GemmParams {
   int M, N, K;
   int m_tiles, n_tiles, k_stages;
   int* status;          // 0 = ok; otherwise the code of the wait that expired
+  // grouped (per-expert) mode: rows of A/out are permuted by expert, B is [E, N, K/2]
+  const int* g_hdr;       // [0] = number of 128-row tiles over all experts
+  const int4* g_mtiles;   // per 128-row tile: {first row, end row of its expert, scale-tile row of A, expert}
+  const float* g_alphas;  // [E]
+  long long g_sfb_expert_bytes;
 };
+
+// What the roles need to know about one output tile.
+struct TileInfo {
+  int a_row0;       // first row of A / out
+  int row_end;      // rows >= row_end are not stored
+  int sfa_tile;     // index of the 128-row scale tile of A
+  int b_row0;       // first row of the (flattened) B matrix
+  int sfb_tile0;    // index of the first 128-row scale tile of B inside its expert
+  int expert;       // -1 in dense mode
+  int n0;           // first output column
+};
+
+template <int BN, bool kGrouped>
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int m_tiles) {
+  TileInfo t;
+  const int mt = tile % m_tiles, nt = tile / m_tiles;
+  t.n0 = nt * BN;
+  t.sfb_tile0 = nt * (BN / 128);
+  if (kGrouped) {
+    const int4 r = p.g_mtiles[mt];
+    t.a_row0 = r.x;
+    t.row_end = r.y;
+    t.sfa_tile = r.z;
+    t.expert = r.w;
+    t.b_row0 = r.w * p.N + nt * BN;
+  } else {
+    t.a_row0 = mt * kBM;
+    t.row_end = p.M;
+    t.sfa_tile = mt;
+    t.expert = -1;
+    t.b_row0 = nt * BN;
+  }
+  return t;
+}
 
 // ---------------------------------------------------------------------------------------- PTX
 
@@ -164,7 +203,7 @@ struct Cfg {
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 };
 
-template <int BN>
+template <int BN, bool kGrouped>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -181,7 +220,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(sf_ready + C::kStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles_total = p.m_tiles * p.n_tiles;
+  const int m_tiles = kGrouped ? p.g_hdr[0] : p.m_tiles;
+  const int n_tiles_total = m_tiles * p.n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -213,23 +253,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
-        const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+        const TileInfo ti = tile_info<BN, kGrouped>(p, tile, m_tiles);
+        const uint8_t* sfb_base = p.sfb + (kGrouped ? (size_t)ti.expert * (size_t)p.g_sfb_expert_bytes : (size_t)0);
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, p.status, 1)) { ok = false; break; }
           unsigned char* st = smem + (size_t)s * C::kStageBytes;
           const int kblocks = min(4, KT - ks * 4);
           int sf_tiles = 0;
-          for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((nt * C::kSfTiles + j) * 128 < p.N) ? 1 : 0;
+          for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((ti.sfb_tile0 + j) * 128 < p.N) ? 1 : 0;
           const uint32_t bar = smem_u32(&full_bar[s]);
           mbar_expect_tx(bar, (uint32_t)(C::kStageA + C::kStageB + kblocks * 512 * (1 + sf_tiles)));
-          tma_load_2d(smem_u32(st), &map_a, ks * kBKBytes, mt * kBM, bar);
-          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * kBKBytes, nt * BN, bar);
-          bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB), p.sfa + ((size_t)mt * KT + (size_t)ks * 4) * 512,
+          tma_load_2d(smem_u32(st), &map_a, ks * kBKBytes, ti.a_row0, bar);
+          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * kBKBytes, ti.b_row0, bar);
+          bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB), p.sfa + ((size_t)ti.sfa_tile * KT + (size_t)ks * 4) * 512,
                        (uint32_t)kblocks * 512, bar);
           for (int j = 0; j < sf_tiles; ++j)
             bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB + C::kStageSFA + j * 2048),
-                         p.sfb + ((size_t)(nt * C::kSfTiles + j) * KT + (size_t)ks * 4) * 512, (uint32_t)kblocks * 512, bar);
+                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * 4) * 512, (uint32_t)kblocks * 512, bar);
         }
       }
     }
@@ -296,17 +337,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;                 // tensor-memory lanes [32*quarter, +32) belong to this warp
-    const float alpha = p.alpha[0];
+    const float alpha_dense = kGrouped ? 0.f : p.alpha[0];
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++tcount) {
-      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+      const TileInfo ti = tile_info<BN, kGrouped>(p, tile, m_tiles);
+      const float alpha = kGrouped ? p.g_alphas[ti.expert] : alpha_dense;
       const uint32_t acc = tcount % C::kAcc, aph = (tcount / C::kAcc) & 1;
       ok = mbar_wait(smem_u32(&acc_full[acc]), aph, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = mt * kBM + quarter * 32 + lane;
+      const int row = ti.a_row0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       // drain this thread's row of the accumulator into packed 16-bit registers ...
       uint32_t packed[BN / 2];
@@ -333,11 +375,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // that the stores overlap the next tile's main loop
       tcgen05_fence_before();
       mbar_arrive(smem_u32(&acc_empty[acc]));
-      if (row < p.M) {
+      if (row < ti.row_end) {
         uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N;
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = nt * BN + c * 32;
+          const int col0 = ti.n0 + c * 32;
           if (col0 < p.N) {
             uint16_t* dst = dst_row + col0;
             if (col0 + 32 <= p.N && (p.N % 8) == 0) {
@@ -362,6 +404,147 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------- grouped helpers
+
+constexpr int kGroupMaxExperts = 4096;
+
+// One block: cuts every expert's row range into 128-row tiles.
+//   hdr[0] = number of tiles; mtiles[t] = {first row, end row of the expert, A scale-tile row, expert}
+__global__ void __launch_bounds__(1024)
+    grouped_tiles_kernel(const int* __restrict__ expert_offsets, const int* __restrict__ sf_offsets, int E, int* hdr,
+                         int4* mtiles, int max_tiles) {
+  __shared__ int s_scan[1024];
+  __shared__ int s_base;
+  const int tid = threadIdx.x;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int e0 = 0; e0 < E; e0 += 1024) {
+    const int e = e0 + tid;
+    int rows = 0, first = 0;
+    if (e < E) {
+      first = expert_offsets[e];
+      rows = expert_offsets[e + 1] - first;
+    }
+    const int nt = (rows + kBM - 1) / kBM;
+    s_scan[tid] = nt;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {          // inclusive Hillis-Steele scan
+      const int v = tid >= d ? s_scan[tid - d] : 0;
+      __syncthreads();
+      s_scan[tid] += v;
+      __syncthreads();
+    }
+    const int start = s_base + s_scan[tid] - nt;
+    if (e < E) {
+      const int sf_row_tile = sf_offsets[e] / 128;
+      for (int i = 0; i < nt; ++i)
+        if (start + i < max_tiles) mtiles[start + i] = make_int4(first + i * kBM, first + rows, sf_row_tile + i, e);
+    }
+    __syncthreads();
+    if (tid == 1023) s_base += s_scan[1023];
+    __syncthreads();
+  }
+  if (tid == 0) hdr[0] = min(s_base, max_tiles);
+}
+
+// Routing metadata for the grouped path (one block): counts pairs per local expert and writes
+//   expert_offsets[E+1]      first permuted row of every expert
+//   blockscale_offsets[E+1]  the same with every expert padded to a multiple of 128 rows
+//   dst2src[P]               permuted row -> pair index (token*topk + slot); -1 past the last valid row
+//   src2dst[P]               pair index -> permuted row, or -1 if the pair's expert is not local
+__global__ void __launch_bounds__(1024)
+    moe_permute_kernel(const int32_t* __restrict__ topk_ids, int P, const int32_t* __restrict__ expert_map, int global_E,
+                       int E, int* expert_offsets, int* blockscale_offsets, int* dst2src, int* src2dst) {
+  __shared__ int s_count[kGroupMaxExperts];
+  __shared__ int s_scan[1024], s_scan2[1024];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += 1024) s_count[e] = 0;
+  __syncthreads();
+  for (int p = tid; p < P; p += 1024) {
+    int e = topk_ids[p];
+    if (expert_map != nullptr) e = (e >= 0 && e < global_E) ? expert_map[e] : -1;
+    if (e < 0 || e >= E) e = -1;
+    src2dst[p] = e;                      // holds the local expert id until the scatter below
+    dst2src[p] = -1;
+    if (e >= 0) atomicAdd(&s_count[e], 1);
+  }
+  __syncthreads();
+  const int per = (E + 1023) / 1024;
+  int sum = 0, sum_pad = 0;
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < E) {
+      sum += s_count[e];
+      sum_pad += (s_count[e] + 127) / 128 * 128;
+    }
+  }
+  s_scan[tid] = sum;
+  s_scan2[tid] = sum_pad;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int v = tid >= d ? s_scan[tid - d] : 0, v2 = tid >= d ? s_scan2[tid - d] : 0;
+    __syncthreads();
+    s_scan[tid] += v;
+    s_scan2[tid] += v2;
+    __syncthreads();
+  }
+  int base = s_scan[tid] - sum, base_pad = s_scan2[tid] - sum_pad;
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < E) {
+      const int c = s_count[e];
+      expert_offsets[e] = base;
+      blockscale_offsets[e] = base_pad;
+      s_count[e] = base;                 // scatter cursor
+      base += c;
+      base_pad += (c + 127) / 128 * 128;
+    }
+  }
+  if (tid == 1023) {
+    expert_offsets[E] = s_scan[1023];
+    blockscale_offsets[E] = s_scan2[1023];
+  }
+  __syncthreads();
+  for (int p = tid; p < P; p += 1024) {
+    const int e = src2dst[p];
+    if (e >= 0) {
+      const int pos = atomicAdd(&s_count[e], 1);
+      src2dst[p] = pos;
+      dst2src[pos] = p;
+    }
+  }
+}
+
+// out[i, :] = in[dst2src[i] / src_div, :] for 16-byte chunks; rows whose map entry is < 0 become zero.
+__global__ void shuffle_rows_kernel(const uint4* __restrict__ in, const int* __restrict__ dst2src, int src_div,
+                                    int64_t chunks_per_row, int64_t n_dst, uint4* __restrict__ out) {
+  const int64_t total = n_dst * chunks_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks_per_row, c = i - r * chunks_per_row;
+    const int src = dst2src[r];
+    out[i] = src >= 0 ? in[(int64_t)(src / src_div) * chunks_per_row + c] : make_uint4(0, 0, 0, 0);
+  }
+}
+
+// out[m, h] = sum over the token's slots of weight * expert_out[src2dst[m*topk + t], h] (local pairs only).
+template <typename T>
+__global__ void unpermute_reduce_kernel(const T* __restrict__ expert_out, const int* __restrict__ src2dst,
+                                        const float* __restrict__ topk_w, int M, int topk, int H, T* __restrict__ out) {
+  const int m = blockIdx.y;
+  for (int h = (blockIdx.x * blockDim.x + threadIdx.x) * 2; h < H; h += gridDim.x * blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int t = 0; t < topk; ++t) {
+      const int r = src2dst[m * topk + t];
+      if (r < 0) continue;
+      const float w = topk_w[m * topk + t];
+      a0 = fmaf(w, to_f32<T>(expert_out[(int64_t)r * H + h]), a0);
+      a1 = fmaf(w, to_f32<T>(expert_out[(int64_t)r * H + h + 1]), a1);
+    }
+    out[(int64_t)m * H + h] = from_f32<T>(a0);
+    out[(int64_t)m * H + h + 1] = from_f32<T>(a1);
   }
 }
 
@@ -399,13 +582,13 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_by
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t st) {
+template <int BN, bool kGrouped>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int max_m_tiles, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)Cfg<BN>::kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
@@ -413,9 +596,10 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cuda
     attr_set[dev] = true;
   }
   p.n_tiles = (p.N + BN - 1) / BN;
-  int grid = p.m_tiles * p.n_tiles;
+  long long grid = (long long)max_m_tiles * p.n_tiles;
   if (grid > sm_count()) grid = sm_count();
-  nvfp4_gemm_kernel<BN><<<grid, kGemmThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
+  if (grid < 1) grid = 1;
+  nvfp4_gemm_kernel<BN, kGrouped><<<(unsigned)grid, kGemmThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -466,7 +650,114 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
   }
-  int rc = bn == 256 ? launch_gemm<256>(ma, mb, p, st) : launch_gemm<128>(ma, mb, p, st);
+  p.g_hdr = nullptr;
+  p.g_mtiles = nullptr;
+  p.g_alphas = nullptr;
+  p.g_sfb_expert_bytes = 0;
+  int rc = bn == 256 ? launch_gemm<256, false>(ma, mb, p, p.m_tiles, st) : launch_gemm<128, false>(ma, mb, p, p.m_tiles, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return finish_launch(2);
+}
+
+// ---------------------------------------------------------------------------------------- grouped entry points
+
+extern "C" size_t b200fp4_grouped_gemm_workspace_bytes(int64_t rows_capacity, int64_t E) {
+  if (rows_capacity < 0 || E < 0) return 0;
+  return 256 + (size_t)(rows_capacity / kBM + E + 1) * sizeof(int4);
+}
+
+extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf,
+                                          const float* alphas, const int32_t* expert_offsets, const int32_t* sf_offsets,
+                                          void* out, int out_dtype, int64_t rows_capacity, int64_t N, int64_t K, int64_t E,
+                                          int tile_n, void* workspace, size_t workspace_bytes, void* stream) {
+  if (rows_capacity < 0 || N <= 0 || K <= 0 || E <= 0 || (K % 64) != 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (out_dtype != B200FP4_DTYPE_BF16 && out_dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (rows_capacity == 0) return B200FP4_STATUS_SUCCESS;
+  if (!a_codes || !b_codes || !a_sf || !b_sf || !alphas || !expert_offsets || !sf_offsets || !out)
+    return B200FP4_STATUS_INVALID_VALUE;
+  if (!aligned(a_codes, 16) || !aligned(b_codes, 16) || !aligned(a_sf, 16) || !aligned(b_sf, 16) || !aligned(out, 16) ||
+      ((K / 2) % 16) != 0)
+    return B200FP4_STATUS_INVALID_VALUE;
+  if (E > kGroupMaxExperts || rows_capacity > (1 << 24) || N > (1 << 20) || K > (1 << 24) || E * N > (int64_t)1 << 30)
+    return B200FP4_STATUS_NOT_SUPPORTED;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return B200FP4_STATUS_INVALID_VALUE;
+  if (!workspace || !aligned(workspace, 16) || workspace_bytes < b200fp4_grouped_gemm_workspace_bytes(rows_capacity, E))
+    return B200FP4_STATUS_ALLOC_FAILED;
+  if (b200fp4_has_hardware_acceleration() != 1) return B200FP4_STATUS_ARCH_MISMATCH;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int max_tiles = (int)(rows_capacity / kBM + E + 1);
+  GemmParams p;
+  p.sfa = reinterpret_cast<const uint8_t*>(a_sf);
+  p.sfb = reinterpret_cast<const uint8_t*>(b_sf);
+  p.alpha = nullptr;
+  p.out = out;
+  p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
+  p.M = (int)rows_capacity; p.N = (int)N; p.K = (int)K;
+  p.m_tiles = max_tiles;
+  p.k_stages = (int)((K + kKPerStage - 1) / kKPerStage);
+  p.status = reinterpret_cast<int*>(workspace);
+  p.g_hdr = reinterpret_cast<int*>(workspace) + 4;
+  p.g_mtiles = reinterpret_cast<const int4*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+  p.g_alphas = alphas;
+  p.g_sfb_expert_bytes = (long long)b200fp4_sf_swizzled_bytes(N, K / 16);
+  // short K means short main loops: prefer the double-buffered narrow tile there
+  int bn = tile_n;
+  if (bn == 0) bn = (K >= 2048 && N % 256 == 0) ? 256 : 128;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a_codes, (uint64_t)rows_capacity, (uint64_t)K / 2, kBM) ||
+      !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, (uint32_t)bn))
+    return B200FP4_STATUS_INTERNAL_ERROR;
+  if (cudaMemsetAsync(workspace, 0, 32, st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  grouped_tiles_kernel<<<1, 1024, 0, st>>>(expert_offsets, sf_offsets, (int)E, const_cast<int*>(p.g_hdr),
+                                           const_cast<int4*>(p.g_mtiles), max_tiles);
+  int rc = bn == 256 ? launch_gemm<256, true>(ma, mb, p, max_tiles, st) : launch_gemm<128, true>(ma, mb, p, max_tiles, st);
+  if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  return finish_launch(3);
+}
+
+extern "C" int b200fp4_moe_permute(const int32_t* topk_ids, const int32_t* expert_map, int64_t global_E, int64_t M,
+                                   int64_t topk, int64_t E, int32_t* expert_offsets, int32_t* blockscale_offsets,
+                                   int32_t* dst2src, int32_t* src2dst, void* stream) {
+  if (M < 0 || topk <= 0 || E <= 0 || E > kGroupMaxExperts || M * topk > (1 << 24)) return B200FP4_STATUS_INVALID_VALUE;
+  if (!expert_offsets || !blockscale_offsets) return B200FP4_STATUS_INVALID_VALUE;
+  if (M > 0 && (!topk_ids || !dst2src || !src2dst)) return B200FP4_STATUS_INVALID_VALUE;
+  if (expert_map && global_E <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  moe_permute_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(topk_ids, (int)(M * topk), expert_map, (int)global_E, (int)E,
+                                                          expert_offsets, blockscale_offsets, dst2src, src2dst);
+  return finish_launch(1);
+}
+
+extern "C" int b200fp4_shuffle_rows(const void* in, int64_t row_bytes, const int32_t* dst2src, int64_t n_dst,
+                                    int64_t src_div, void* out, void* stream) {
+  if (n_dst < 0 || row_bytes <= 0 || (row_bytes % 16) != 0 || src_div <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (n_dst == 0) return B200FP4_STATUS_SUCCESS;
+  if (!in || !dst2src || !out || !aligned(in, 16) || !aligned(out, 16)) return B200FP4_STATUS_INVALID_VALUE;
+  const int64_t total = n_dst * (row_bytes / 16);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 16 * (int64_t)sm_count()) blocks = 16 * (int64_t)sm_count();
+  shuffle_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const uint4*>(in), dst2src, (int)src_div, row_bytes / 16, n_dst, reinterpret_cast<uint4*>(out));
+  return finish_launch(1);
+}
+
+extern "C" int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, const int32_t* src2dst,
+                                            const float* topk_weights, int64_t M, int64_t topk, int64_t H, void* out,
+                                            void* stream) {
+  if (M < 0 || topk <= 0 || H <= 0 || (H % 2) != 0 || M > 65535) return B200FP4_STATUS_INVALID_VALUE;
+  if (dtype != B200FP4_DTYPE_BF16 && dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (M == 0) return B200FP4_STATUS_SUCCESS;
+  if (!expert_out || !src2dst || !topk_weights || !out) return B200FP4_STATUS_INVALID_VALUE;
+  dim3 grid((unsigned)((H / 2 + 127) / 128), (unsigned)M);
+  if (dtype == B200FP4_DTYPE_BF16)
+    unpermute_reduce_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(expert_out), src2dst, topk_weights, (int)M, (int)topk, (int)H,
+        reinterpret_cast<__nv_bfloat16*>(out));
+  else
+    unpermute_reduce_kernel<__half><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __half*>(expert_out), src2dst, topk_weights, (int)M, (int)topk, (int)H,
+        reinterpret_cast<__half*>(out));
+  return finish_launch(1);
 }

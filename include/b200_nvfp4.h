@@ -196,6 +196,51 @@ B200FP4_API int b200fp4_fused_sparse_moe(
     int out_dtype, int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
     int apply_router_weight_on_input, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Part 4 -- grouped (per-expert) NVFP4 GEMM for MoE prefill and its routing helpers.
+ * The reference's own grouped kernel is an FP8 CUTLASS configuration behind
+ * extern "C" cutlass_moe_mm_gb10(out, a, b, a_scales, b_scales, expert_offsets, problem_sizes,
+ * strides..., per_act_token, per_out_ch) (grouped_mm_gb10_native.cu:196-208; tile policy :44-100,
+ * :141-156); the NVFP4 contract mirrored here is the upstream op that path stands in for,
+ * cutlass_fp4_group_mm(out, a, b, a_scales, b_scales, alphas, problem_sizes, expert_offsets,
+ * sf_offsets) with get_cutlass_moe_mm_data / shuffle_rows (vllm/_custom_ops.py:854-933,1017-1054).
+ * ------------------------------------------------------------------------------------------- */
+
+/* get_cutlass_moe_mm_data: group the M*topk (token, expert) pairs by local expert.
+ *   expert_offsets[E+1], blockscale_offsets[E+1] (each expert padded to 128 rows),
+ *   dst2src[M*topk]: permuted row -> pair index token*topk+slot (-1 past the last valid row),
+ *   src2dst[M*topk]: pair index -> permuted row (-1 when the pair's expert is not local).
+ * expert_map [global_E] or NULL as in b200fp4_fused_sparse_moe. */
+B200FP4_API int b200fp4_moe_permute(const int32_t* topk_ids, const int32_t* expert_map,
+                                    int64_t global_E, int64_t M, int64_t topk, int64_t E,
+                                    int32_t* expert_offsets, int32_t* blockscale_offsets,
+                                    int32_t* dst2src, int32_t* src2dst, void* stream);
+
+/* shuffle_rows: out[i,:] = in[dst2src[i] / src_div, :] (rows of row_bytes bytes, multiple of 16);
+ * negative map entries give zero rows. */
+B200FP4_API int b200fp4_shuffle_rows(const void* in, int64_t row_bytes, const int32_t* dst2src,
+                                     int64_t n_dst, int64_t src_div, void* out, void* stream);
+
+/* cutlass_fp4_group_mm: rows [expert_offsets[e], expert_offsets[e+1]) of a (packed codes
+ * [rows_capacity, K/2], scales swizzled with expert e's rows starting at sf_offsets[e]) times
+ * expert e's weight b[e] ([E, N, K/2] codes, b_sf [E, swizzled(N, K/16)]), scaled by alphas[e],
+ * into out[rows_capacity, N].  Rows past expert_offsets[E] are not written.  The first int of the
+ * workspace is the same status word as for b200fp4_gemm_nvfp4. */
+B200FP4_API size_t b200fp4_grouped_gemm_workspace_bytes(int64_t rows_capacity, int64_t E);
+B200FP4_API int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* a_sf,
+                                           const void* b_sf, const float* alphas,
+                                           const int32_t* expert_offsets, const int32_t* sf_offsets,
+                                           void* out, int out_dtype, int64_t rows_capacity, int64_t N,
+                                           int64_t K, int64_t E, int tile_n, void* workspace,
+                                           size_t workspace_bytes, void* stream);
+
+/* Un-permute and router-weighted sum: out[m,:] = sum_t w[m,t] * expert_out[src2dst[m*topk+t], :]
+ * over local pairs (the shuffle_rows + weighted sum at the end of
+ * vllm/model_executor/layers/fused_moe/experts/cutlass_moe.py:567-663). */
+B200FP4_API int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, const int32_t* src2dst,
+                                             const float* topk_weights, int64_t M, int64_t topk,
+                                             int64_t H, void* out, void* stream);
+
 /* Benchmark hook (no counterpart in the reference): when the three cudaEvent_t handles are non-NULL,
  * b200fp4_fused_sparse_moe records them on its stream before the gate_up GEMV, between the two
  * GEMVs and after the down GEMV, so a caller can time the two dominant kernels inside a fused
