@@ -27,8 +27,6 @@ namespace b200fp4 {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kBKBytes = 128;             // bytes of packed codes per row per stage (= 256 k)
-constexpr int kKPerStage = 256;
 constexpr int kGemmThreads = 320;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale factors
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000LL;   // ~1 s at 2 GHz
@@ -174,40 +172,46 @@ __device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::
 
 // Shared-memory matrix descriptors (K-major).  Fields: start address >> 4 in bits [0,14), leading
 // byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in
-// [46,48), swizzle mode in [61,64) (2 = 128-byte swizzle).
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-  // rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+// [46,48), swizzle mode in [61,64) (2 = 128-byte, 4 = 64-byte, 6 = 32-byte swizzle).
+// Rows of kRowBytes (128, 64 or 32) bytes with the matching swizzle; 8-row atoms are 8*kRowBytes apart.
+template <int kRowBytes>
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  constexpr uint64_t mode = kRowBytes == 128 ? 2ull : (kRowBytes == 64 ? 4ull : 6ull);
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)((8 * kRowBytes) >> 4) << 32) | (1ull << 46) |
+         (mode << 61);
 }
 
 // ---------------------------------------------------------------------------------------- kernel
 
-template <int BN>
+// BN = tile width; KB = 64-wide k-blocks (MMAs) per shared-memory stage.  Smaller stages do not change
+// the bytes resident in shared memory but refill in finer steps, which keeps more of them in flight.
+template <int BN, int KB>
 struct Cfg {
   static constexpr int kAcc = BN == 128 ? 2 : 1;                    // accumulator buffers in tensor memory
   static constexpr int kSfTiles = BN / 128;                         // 128-row scale tiles on the B side
-  static constexpr int kStageA = kBM * kBKBytes;                    // 16 KiB
-  static constexpr int kStageB = BN * kBKBytes;
-  static constexpr int kStageSFA = 4 * 512;
-  static constexpr int kStageSFB = kSfTiles * 4 * 512;
+  static constexpr int kRowBytes = KB * 32;                         // packed codes per row per stage
+  static constexpr int kStageA = kBM * kRowBytes;
+  static constexpr int kStageB = BN * kRowBytes;
+  static constexpr int kStageSFA = KB * 512;
+  static constexpr int kStageSFB = kSfTiles * KB * 512;
   static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
-  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kStages = (BN == 128 ? 24 : 16) / KB;
   // tensor-memory column map: accumulators, then one scale-factor block per shared-memory stage
-  // (16 columns for A, 16*kSfTiles for B) so that the tcgen05.cp of stage s+1 never has to wait
-  // for the MMAs of stage s to finish reading their scales
-  static constexpr uint32_t kSfCols = 16 + 16 * kSfTiles;
+  // (4 columns per k-block for A, 4*kSfTiles for B)
+  static constexpr uint32_t kSfCols = KB * (4 + 4 * kSfTiles);
   static constexpr uint32_t kSfBase = kAcc * BN;
   static_assert(kSfBase + kStages * kSfCols <= 512, "tensor memory budget");
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kBarBytes = 1024;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + kBarBytes;
   // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major A and B, N = BN, M = 128, dense K = 64
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 };
 
-template <int BN, bool kGrouped>
+template <int BN, int KB, bool kGrouped>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, KB>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -259,18 +263,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, p.status, 1)) { ok = false; break; }
           unsigned char* st = smem + (size_t)s * C::kStageBytes;
-          const int kblocks = min(4, KT - ks * 4);
+          const int kblocks = min(KB, KT - ks * KB);
           int sf_tiles = 0;
           for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((ti.sfb_tile0 + j) * 128 < p.N) ? 1 : 0;
           const uint32_t bar = smem_u32(&full_bar[s]);
           mbar_expect_tx(bar, (uint32_t)(C::kStageA + C::kStageB + kblocks * 512 * (1 + sf_tiles)));
-          tma_load_2d(smem_u32(st), &map_a, ks * kBKBytes, ti.a_row0, bar);
-          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * kBKBytes, ti.b_row0, bar);
-          bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB), p.sfa + ((size_t)ti.sfa_tile * KT + (size_t)ks * 4) * 512,
+          tma_load_2d(smem_u32(st), &map_a, ks * C::kRowBytes, ti.a_row0, bar);
+          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
+          bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB), p.sfa + ((size_t)ti.sfa_tile * KT + (size_t)ks * KB) * 512,
                        (uint32_t)kblocks * 512, bar);
           for (int j = 0; j < sf_tiles; ++j)
-            bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB + C::kStageSFA + j * 2048),
-                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * 4) * 512, (uint32_t)kblocks * 512, bar);
+            bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB + C::kStageSFA + j * (KB * 512)),
+                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * KB) * 512, (uint32_t)kblocks * 512, bar);
         }
       }
     }
@@ -289,15 +293,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, p.status, 3)) { ok = false; break; }
           tcgen05_fence_after();
           unsigned char* st = smem + (size_t)s * C::kStageBytes;
-          const int kblocks = min(4, KT - ks * 4);
+          const int kblocks = min(KB, KT - ks * KB);
           const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + C::kStageA);
-          const uint32_t sfa_tmem = tmem_base + C::kSfBase + s * C::kSfCols, sfb_tmem = sfa_tmem + 16;
+          const uint32_t sfa_tmem = tmem_base + C::kSfBase + s * C::kSfCols, sfb_tmem = sfa_tmem + 4 * KB;
           if (!mbar_wait(smem_u32(&sf_ready[s]), ph, p.status, 5)) { ok = false; break; }
           tcgen05_fence_after();
           for (int kb = 0; kb < kblocks; ++kb) {
             // each 64-wide k-block is 32 bytes further along the swizzled 128-byte rows
-            tcgen05_mma_nvf4(d_tmem, desc_sw128(a_addr + kb * 32), desc_sw128(b_addr + kb * 32), C::kIdesc,
-                             sfa_tmem + kb * 4, sfb_tmem + kb * (4 * C::kSfTiles), (ks > 0 || kb > 0) ? 1u : 0u);
+            tcgen05_mma_nvf4(d_tmem, desc_kmajor<C::kRowBytes>(a_addr + kb * 32), desc_kmajor<C::kRowBytes>(b_addr + kb * 32),
+                             C::kIdesc, sfa_tmem + kb * 4, sfb_tmem + kb * (4 * C::kSfTiles), (ks > 0 || kb > 0) ? 1u : 0u);
           }
           tcgen05_commit(smem_u32(&empty_bar[s]));    // frees the stage when these MMAs have read it
         }
@@ -321,13 +325,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!ok) break;
         const unsigned char* sf = smem + (size_t)s * C::kStageBytes + C::kStageA + C::kStageB;
         const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kSfBase + s * C::kSfCols;
-        const int kblocks = min(4, KT - ks * 4);
+        const int kblocks = min(KB, KT - ks * KB);
         for (int kb = 0; kb < kblocks; ++kb) {
           tcgen05_st_32x32_x4(t0 + kb * 4, *reinterpret_cast<const uint4*>(sf + kb * 512 + lane * 16));
 #pragma unroll
           for (int j = 0; j < C::kSfTiles; ++j)
-            tcgen05_st_32x32_x4(t0 + 16 + kb * (4 * C::kSfTiles) + j * 4,
-                                *reinterpret_cast<const uint4*>(sf + C::kStageSFA + j * 2048 + kb * 512 + lane * 16));
+            tcgen05_st_32x32_x4(t0 + 4 * KB + kb * (4 * C::kSfTiles) + j * 4,
+                                *reinterpret_cast<const uint4*>(sf + C::kStageSFA + j * (KB * 512) + kb * 512 + lane * 16));
         }
         tcgen05_wait_st();
         tcgen05_fence_before();
@@ -569,27 +573,29 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, row_bytes] u8 row-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill out of bounds
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+// [rows, row_bytes] u8 row-major; box = box_bytes (128/64/32) x box_rows with the matching swizzle, zero fill out of bounds
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, int box_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {row_bytes, rows};
   cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)kBKBytes, box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_bytes, box_rows};
+  const CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : (box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, bool kGrouped>
+template <int BN, int KB, bool kGrouped>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int max_m_tiles, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Cfg<BN>::kSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, KB, kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)Cfg<BN, KB>::kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
@@ -599,8 +605,22 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int 
   long long grid = (long long)max_m_tiles * p.n_tiles;
   if (grid > sm_count()) grid = sm_count();
   if (grid < 1) grid = 1;
-  nvfp4_gemm_kernel<BN, kGrouped><<<(unsigned)grid, kGemmThreads, Cfg<BN>::kSmemBytes, st>>>(ma, mb, p);
+  p.k_stages = (p.K + KB * 64 - 1) / (KB * 64);
+  nvfp4_gemm_kernel<BN, KB, kGrouped><<<(unsigned)grid, kGemmThreads, Cfg<BN, KB>::kSmemBytes, st>>>(ma, mb, p);
   return B200FP4_STATUS_SUCCESS;
+}
+
+// 64-wide k-blocks per shared-memory stage.  The kernel template also builds with 2 or 1 (64- and
+// 32-byte swizzled rows, 8 or 16 stages); on B200 those measured 190 and 317 us against 150 us at
+// M=4096 (TMA issues one request per box row, so narrower rows double and quadruple the requests).
+int stage_kblocks() { return 4; }
+
+template <bool kGrouped>
+int dispatch_gemm(int bn, int kb, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_m_tiles,
+                  cudaStream_t st) {
+  (void)kb;
+  if (bn == 256) return launch_gemm<256, 4, kGrouped>(ma, mb, p, max_m_tiles, st);
+  return launch_gemm<128, 4, kGrouped>(ma, mb, p, max_m_tiles, st);
 }
 
 }  // namespace
@@ -636,15 +656,15 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.m_tiles = (int)((M + kBM - 1) / kBM);
-  p.k_stages = (int)((K + kKPerStage - 1) / kKPerStage);
   p.status = reinterpret_cast<int*>(workspace);
   // Wide tiles once there are enough of them to fill the GPU; narrow tiles (double-buffered
   // accumulator, twice the CTAs) for small problems.
   int bn = tile_n;
   if (bn == 0) bn = (p.m_tiles * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
+  const int kb = stage_kblocks();
   CUtensorMap ma, mb;
-  if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM) ||
-      !make_map(&mb, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn))
+  if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM, kb * 32) ||
+      !make_map(&mb, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn, kb * 32))
     return B200FP4_STATUS_INTERNAL_ERROR;
   if (cudaMemsetAsync(workspace, 0, 16, st) != cudaSuccess) {
     cudaGetLastError();
@@ -654,7 +674,7 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   p.g_mtiles = nullptr;
   p.g_alphas = nullptr;
   p.g_sfb_expert_bytes = 0;
-  int rc = bn == 256 ? launch_gemm<256, false>(ma, mb, p, p.m_tiles, st) : launch_gemm<128, false>(ma, mb, p, p.m_tiles, st);
+  int rc = dispatch_gemm<false>(bn, kb, ma, mb, p, p.m_tiles, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return finish_launch(2);
 }
@@ -694,7 +714,6 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
   p.M = (int)rows_capacity; p.N = (int)N; p.K = (int)K;
   p.m_tiles = max_tiles;
-  p.k_stages = (int)((K + kKPerStage - 1) / kKPerStage);
   p.status = reinterpret_cast<int*>(workspace);
   p.g_hdr = reinterpret_cast<int*>(workspace) + 4;
   p.g_mtiles = reinterpret_cast<const int4*>(reinterpret_cast<unsigned char*>(workspace) + 256);
@@ -703,9 +722,10 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   // short K means short main loops: prefer the double-buffered narrow tile there
   int bn = tile_n;
   if (bn == 0) bn = (K >= 2048 && N % 256 == 0) ? 256 : 128;
+  const int kb = stage_kblocks();
   CUtensorMap ma, mb;
-  if (!make_map(&ma, a_codes, (uint64_t)rows_capacity, (uint64_t)K / 2, kBM) ||
-      !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, (uint32_t)bn))
+  if (!make_map(&ma, a_codes, (uint64_t)rows_capacity, (uint64_t)K / 2, kBM, kb * 32) ||
+      !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, (uint32_t)bn, kb * 32))
     return B200FP4_STATUS_INTERNAL_ERROR;
   if (cudaMemsetAsync(workspace, 0, 32, st) != cudaSuccess) {
     cudaGetLastError();
@@ -713,7 +733,7 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   }
   grouped_tiles_kernel<<<1, 1024, 0, st>>>(expert_offsets, sf_offsets, (int)E, const_cast<int*>(p.g_hdr),
                                            const_cast<int4*>(p.g_mtiles), max_tiles);
-  int rc = bn == 256 ? launch_gemm<256, true>(ma, mb, p, max_tiles, st) : launch_gemm<128, true>(ma, mb, p, max_tiles, st);
+  int rc = dispatch_gemm<true>(bn, kb, ma, mb, p, max_tiles, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return finish_launch(3);
 }

@@ -1,7 +1,8 @@
 // bf16/f16 -> NVFP4 quantizer for sm_100a.
 //
 // One thread owns 8 consecutive elements (one 16-byte load); two neighbouring lanes form one
-// 16-element scale block and share the block maximum through a warp shuffle.  Codes leave as one
+// 16-element scale block and share the block maximum (found with packed 16-bit max) through a warp
+// shuffle.  The per-block reciprocal depends only on the scale byte, so it is tabulated per block.  Codes leave as one
 // 4-byte store per thread, so a warp reads 512 contiguous bytes per row segment and writes 128.
 // Arithmetic follows ref_nvfp4_quant (vllm/model_executor/layers/quantization/utils/
 // nvfp4_emulation_utils.py:439-453) operation by operation in IEEE fp32 -- explicit _rn
@@ -21,14 +22,49 @@ constexpr int kTX = 64;    // threads along K (each 8 elements): 512 elements pe
 constexpr int kTY = 4;     // rows per block per pass
 constexpr int kRows = 4;   // passes (rows) per thread, loads issued together
 
+// Packed helpers on two 16-bit floats in one register.
+template <typename T>
+struct Pk;
+template <>
+struct Pk<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+};
+template <>
+struct Pk<__half> {
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ float lo(uint32_t w) { return __low2float(*reinterpret_cast<const __half2*>(&w)); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __high2float(*reinterpret_cast<const __half2*>(&w)); }
+};
+
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& raw, float* v) {
-  const T* h = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(h[i]);
+  v[0] = Pk<T>::lo(raw.x); v[1] = Pk<T>::hi(raw.x); v[2] = Pk<T>::lo(raw.y); v[3] = Pk<T>::hi(raw.y);
+  v[4] = Pk<T>::lo(raw.z); v[5] = Pk<T>::hi(raw.z); v[6] = Pk<T>::lo(raw.w); v[7] = Pk<T>::hi(raw.w);
+}
+
+// max |x| over the 8 packed values (exact: the maximum of 16-bit floats is one of them)
+template <typename T>
+__device__ __forceinline__ float amax8(const uint4& raw) {
+  const uint32_t m = 0x7FFF7FFFu;
+  const uint32_t w = Pk<T>::max2(Pk<T>::max2(raw.x & m, raw.y & m), Pk<T>::max2(raw.z & m, raw.w & m));
+  return fmaxf(Pk<T>::lo(w), Pk<T>::hi(w));
 }
 
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+
+// 1 / (decoded block scale / global scale), with the reference's "x == 0 -> x + 1e8" guards
+__device__ __forceinline__ float out_scale_of(uint8_t sfb, float rcp_gs) {
+  const float t = __fmul_rn(e4m3_to_f32(sfb), rcp_gs);
+  return __frcp_rn(t + (t == 0.f ? 1.0e8f : 0.f));
+}
 
 // kExperts: per-row expert lookup (global scale + scale-factor row offset per expert).
 // kSilu:    input is [M, 2K]; quantize round_to_T(silu(x[:, :K]) * x[:, K:]).
@@ -56,24 +92,37 @@ __global__ void __launch_bounds__(kTX* kTY)
     }
   }
 
+  // With one global scale for the whole call the multiplier applied to the elements depends only on the
+  // block-scale byte (127 values): each block tabulates it once with the exact arithmetic.
+  __shared__ float s_os[128];
   float gs_shared = 0.f;
-  if (!kExperts) gs_shared = gs_ptr[0];
+  if (!kExperts) {
+    gs_shared = gs_ptr[0];
+    const int t = threadIdx.y * kTX + threadIdx.x;
+    if (t < 128) s_os[t] = out_scale_of((uint8_t)t, __frcp_rn(gs_shared + (gs_shared == 0.f ? 1.0e8f : 0.f)));
+    __syncthreads();
+  }
 
 #pragma unroll
   for (int r = 0; r < kRows; ++r) {
     const int64_t m = m0 + r;
     const bool ok = col_ok && m < M;
     float v[8];
-    unpack8<T>(raw[r], v);
+    float amax;
     if (kSilu) {
       float u[8];
+      unpack8<T>(raw[r], v);
       unpack8<T>(raw2[r], u);
+      amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = to_f32<T>(from_f32<T>(silu_f32(v[i]) * u[i]));
+      for (int i = 0; i < 8; ++i) {
+        v[i] = to_f32<T>(from_f32<T>(silu_f32(v[i]) * u[i]));
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+    } else {
+      amax = amax8<T>(raw[r]);
+      unpack8<T>(raw[r], v);
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
 
     float gs = gs_shared;
@@ -92,12 +141,12 @@ __global__ void __launch_bounds__(kTX* kTY)
       }
     }
 
-    const float rcp_gs = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
     float scale = __fmul_rn(gs, __fmul_rn(amax, 0.16666667163372039794921875f));  // fl32(1/6)
     scale = fminf(scale, 448.f);
     const uint8_t sfb = f32_to_e4m3(scale);
-    const float t = __fmul_rn(e4m3_to_f32(sfb), rcp_gs);
-    const float os = __frcp_rn(t + (t == 0.f ? 1.0e8f : 0.f));
+    float os;
+    if (kExperts) os = out_scale_of(sfb, __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f)));
+    else os = s_os[sfb & 127];
 
     const uint32_t packed =
         f32x8_to_e2m1(__fmul_rn(v[0], os), __fmul_rn(v[1], os), __fmul_rn(v[2], os), __fmul_rn(v[3], os),

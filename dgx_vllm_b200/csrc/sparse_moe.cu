@@ -26,8 +26,7 @@ extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E
 namespace b200fp4 {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
+constexpr int kThreads = 256;      // block size of the 16-columns-per-thread variant
 constexpr int kMaxTok = 4;       // tokens of one expert processed per pass over its weights
 constexpr int kPlanThreads = 1024;
 constexpr int kPlanMaxExperts = 4096;
@@ -200,8 +199,8 @@ __device__ __forceinline__ uint32_t e2m1_to_half_bits(uint32_t nib) {
 // Row b (256 bytes) of the table: words 0..31 hold 32 copies of the half2 pair decoded from the
 // compressed byte b, words 32..63 hold 32 copies of the two PRMT selectors decoded from the
 // metadata byte b.  A lane always reads word `lane` (or 32+lane), i.e. its own bank.
-__device__ __forceinline__ void fill_tables(uint32_t* lut, int tid) {
-  for (int b = tid; b < 256; b += kThreads) {
+__device__ __forceinline__ void fill_tables(uint32_t* lut, int tid, int nthreads) {
+  for (int b = tid; b < 256; b += nthreads) {
     const uint32_t vc = e2m1_to_half_bits(b & 15) | (e2m1_to_half_bits(b >> 4) << 16);
     const uint32_t i0 = b & 3, i1 = (b >> 2) & 3, i2 = (b >> 4) & 3, i3 = (b >> 6) & 3;
     const uint32_t s0 = (2 * i0) | ((2 * i0 + 1) << 4) | ((2 * i1) << 8) | ((2 * i1 + 1) << 12);
@@ -222,6 +221,16 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+// COLS bytes (16 or 8) of one weight row
+template <int COLS>
+__device__ __forceinline__ void cp_async_cols(void* smem_dst, const void* gmem_src) {
+  if (COLS == 16) cp_async16(smem_dst, gmem_src);
+  else cp_async8(smem_dst, gmem_src);
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -236,15 +245,15 @@ __device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *rein
 
 // One scale block (16 k) x 16 columns for T tokens.  v[] = 4 compressed rows, 2 metadata rows,
 // 1 (or 2) scale rows; a[t] = the 16 activations of token t as 8 half2.
-template <int T, bool kScale8>
+template <int T, int COLS, bool kScale8>
 __device__ __forceinline__ void compute_block(const uint4 (&v)[8], const uint4 (&a)[T][2], const unsigned char* lut,
-                                              uint32_t lane4, float (&acc)[T][16]) {
+                                              uint32_t lane4, float (&acc)[T][COLS]) {
   // PRMT selectors: (table row = byte j of the word) << 8 | lane*4
   constexpr uint32_t kIdx[4] = {0x5504u, 0x5514u, 0x5524u, 0x5534u};
   // PRMT selectors: bytes (j, j+1) of the scale word to the high bytes of two halves
   constexpr uint32_t kSc[2] = {0x1404u, 0x3424u};
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
+  for (int q = 0; q < COLS / 4; ++q) {
     const uint32_t c0 = word_of(v[0], q), c1 = word_of(v[1], q), c2 = word_of(v[2], q), c3 = word_of(v[3], q);
     const uint32_t m0 = word_of(v[4], q), m1 = word_of(v[5], q);
     const uint32_t s0 = word_of(v[6], q) & 0x7F7F7F7Fu;
@@ -311,18 +320,23 @@ __device__ __forceinline__ Rec empty_rec() {
   return r;
 }
 
-// CG      16-column groups per slab (8, 16 or 32): slab = 16*CG columns, 256/CG K-slices
-// S       cp.async ring stages (2 or 3); every thread must own at least S-1 scale blocks per item
+// NT      threads per block: 256 with COLS = 16 columns per thread, or 512 with COLS = 8 (twice the
+//         warps per SM for latency hiding, half the accumulators per thread)
+// CG      column groups per slab: slab = COLS*CG columns, NT/CG K-slices
+// S       cp.async ring stages; every thread must own at least S-1 scale blocks per item
 // kScale8 one scale per 8 k instead of per 16 k
 // kSilu   slab = CG*8 gate columns + the matching CG*8 up columns; epilogue writes SiLU(gate)*up
-template <int CG, int S, bool kScale8, bool kSilu>
-__global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs g) {
+template <int NT, int COLS, int CG, int S, bool kScale8, bool kSilu>
+__global__ void __launch_bounds__(NT, 1) sparse_gemv_kernel(const GemvArgs g) {
+  constexpr int kThreads = NT;
+  constexpr int kWarps = NT / 32;
   constexpr int KS = kThreads / CG;
-  constexpr int SLAB = CG * 16;
+  constexpr int SLAB = CG * COLS;
   constexpr int NV = kScale8 ? 8 : 7;
+  using Vec = typename std::conditional<COLS == 16, uint4, uint2>::type;   // COLS bytes of one weight row
   extern __shared__ __align__(16) unsigned char smem[];
   uint32_t* lut_w = reinterpret_cast<uint32_t*>(smem);
-  uint4* ring = reinterpret_cast<uint4*>(smem + kLutBytes);                      // [S][NV][256]
+  Vec* ring = reinterpret_cast<Vec*>(smem + kLutBytes);                          // [S][NV][NT]
   float* red = reinterpret_cast<float*>(ring + S * NV * kThreads);               // [kWarps][kMaxTok][SLAB]
   __half* sA = reinterpret_cast<__half*>(red + kWarps * kMaxTok * SLAB);         // [2][kMaxTok][K]
 
@@ -334,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
   const int K = g.K, KB = K >> 4;
   const int nblk = (KB - kslice + KS - 1) / KS;   // scale blocks this thread owns in every item (>= S-1)
   const int grid = gridDim.x;
-  fill_tables(lut_w, tid);
+  fill_tables(lut_w, tid, kThreads);
 
   const int n_items = g.plan.hdr[1] * g.n_slabs;
   int item = blockIdx.x;
@@ -362,8 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
         const int e = (f_item == item) ? cur.e : nxt.e;
         const int slab = f_item % g.n_slabs;
         int col0;
-        if (kSilu) col0 = (cg < CG / 2) ? slab * (SLAB / 2) + cg * 16 : g.inter + slab * (SLAB / 2) + (cg - CG / 2) * 16;
-        else col0 = slab * SLAB + cg * 16;
+        if (kSilu) col0 = (cg < CG / 2) ? slab * (SLAB / 2) + cg * COLS : g.inter + slab * (SLAB / 2) + (cg - CG / 2) * COLS;
+        else col0 = slab * SLAB + cg * COLS;
         f_ok = kSilu ? ((cg < CG / 2 ? col0 : col0 - g.inter) < g.inter) : (col0 < g.N);
         f_comp = g.w.comp + (int64_t)e * g.w.comp_e + col0;
         f_meta = g.w.meta + (int64_t)e * g.w.meta_e + col0;
@@ -371,21 +385,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
       }
       if (f_ok) {
         const int kb = kslice + KS * f_j;
-        uint4* dst = ring + (size_t)f_slot * NV * kThreads + tid;
+        Vec* dst = ring + (size_t)f_slot * NV * kThreads + tid;
         const uint8_t* c0 = f_comp + (int64_t)(2 * kb) * g.w.comp_pair;
-        cp_async16(dst, c0);
-        cp_async16(dst + kThreads, c0 + g.w.comp_odd);
-        cp_async16(dst + 2 * kThreads, c0 + g.w.comp_pair);
-        cp_async16(dst + 3 * kThreads, c0 + g.w.comp_pair + g.w.comp_odd);
+        cp_async_cols<COLS>(dst, c0);
+        cp_async_cols<COLS>(dst + kThreads, c0 + g.w.comp_odd);
+        cp_async_cols<COLS>(dst + 2 * kThreads, c0 + g.w.comp_pair);
+        cp_async_cols<COLS>(dst + 3 * kThreads, c0 + g.w.comp_pair + g.w.comp_odd);
         const uint8_t* m0 = f_meta + (int64_t)(2 * kb) * g.w.meta_row;
-        cp_async16(dst + 4 * kThreads, m0);
-        cp_async16(dst + 5 * kThreads, m0 + g.w.meta_row);
+        cp_async_cols<COLS>(dst + 4 * kThreads, m0);
+        cp_async_cols<COLS>(dst + 5 * kThreads, m0 + g.w.meta_row);
         if (kScale8) {
           const uint8_t* s0 = f_scale + (int64_t)(2 * kb) * g.w.scale_row;
-          cp_async16(dst + 6 * kThreads, s0);
-          cp_async16(dst + 7 * kThreads, s0 + g.w.scale_row);
+          cp_async_cols<COLS>(dst + 6 * kThreads, s0);
+          cp_async_cols<COLS>(dst + 7 * kThreads, s0 + g.w.scale_row);
         } else {
-          cp_async16(dst + 6 * kThreads, f_scale + (int64_t)kb * g.w.scale_row);
+          cp_async_cols<COLS>(dst + 6 * kThreads, f_scale + (int64_t)kb * g.w.scale_row);
         }
       }
       if (++f_j == nblk) {
@@ -413,20 +427,30 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
     __syncthreads();          // sA[abuf] complete for all threads; red and sA[abuf^1] free
     issue_A(rn, abuf ^ 1);
 
-    float accs[kMaxTok][16];
+    float accs[kMaxTok][COLS];
     auto run = [&](auto tconst) {
       constexpr int T = decltype(tconst)::value;
-      float acc[T][16];
+      float acc[T][COLS];
 #pragma unroll
       for (int t = 0; t < T; ++t)
 #pragma unroll
-        for (int c = 0; c < 16; ++c) acc[t][c] = 0.f;
+        for (int c = 0; c < COLS; ++c) acc[t][c] = 0.f;
       for (int j = 0; j < nblk; ++j) {
         cp_async_wait<S - 2>();
         uint4 v[8];
-        const uint4* src = ring + (size_t)c_slot * NV * kThreads + tid;
+        const Vec* src = ring + (size_t)c_slot * NV * kThreads + tid;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) v[i] = src[i * kThreads];
+        for (int i = 0; i < NV; ++i) {
+          const Vec x = src[i * kThreads];
+          v[i].x = x.x;
+          v[i].y = x.y;
+          if (COLS == 16) {
+            v[i].z = reinterpret_cast<const uint32_t*>(&x)[COLS == 16 ? 2 : 0];
+            v[i].w = reinterpret_cast<const uint32_t*>(&x)[COLS == 16 ? 3 : 0];
+          } else {
+            v[i].z = v[i].w = 0u;
+          }
+        }
         if (!kScale8) v[7] = make_uint4(0, 0, 0, 0);
         fetch_next(rc, rn);
         const int kb = kslice + KS * j;
@@ -437,14 +461,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
           a[t][0] = pa[0];
           a[t][1] = pa[1];
         }
-        compute_block<T, kScale8>(v, a, smem, lane4, acc);
+        compute_block<T, COLS, kScale8>(v, a, smem, lane4, acc);
         c_slot = (c_slot + 1 == S) ? 0 : c_slot + 1;
       }
       // K reduction: the K-slices of a warp through shuffles, then the warps through shared memory
 #pragma unroll
       for (int t = 0; t < T; ++t)
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < COLS; ++c) {
           float x = acc[t][c];
 #pragma unroll
           for (int d = CG; d < 32; d <<= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
@@ -453,9 +477,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_gemv_kernel(const GemvArgs
       if (ksub == 0) {
 #pragma unroll
         for (int t = 0; t < T; ++t) {
-          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * kMaxTok + t) * SLAB + cg * 16);
+          float4* dst = reinterpret_cast<float4*>(red + ((size_t)warp * kMaxTok + t) * SLAB + cg * COLS);
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < COLS / 4; ++c)
             dst[c] = make_float4(accs[t][4 * c], accs[t][4 * c + 1], accs[t][4 * c + 2], accs[t][4 * c + 3]);
         }
       }
@@ -604,23 +628,32 @@ Plan carve_plan(void* ws, int64_t P, int64_t E) {
 }
 
 struct GemvCfg {
-  int cg, stages;
+  int nt, cols, cg, stages;
   size_t smem;
   bool ok;
 };
 
+size_t gemv_smem(int nt, int cols, int cg, int stages, bool scale8, int64_t K) {
+  const int nv = scale8 ? 8 : 7;
+  return (size_t)kLutBytes + (size_t)stages * nv * nt * cols + (size_t)(nt / 32) * kMaxTok * cg * cols * 4 +
+         (size_t)2 * kMaxTok * K * 2;
+}
+
+// Picks slab shape and ring depth for a K.  Every thread must own >= stages-1 scale blocks per item.
+// (The kernel template also builds as 512 threads x 8 columns per thread; on B200 that variant
+// measured 20 % slower at batch 32 -- 177 vs 148 us per layer -- so it is not instantiated.)
 GemvCfg pick_cfg(int64_t K, bool scale8) {
-  GemvCfg c = {0, 0, 0, false};
+  GemvCfg c = {0, 0, 0, 0, 0, false};
   const int64_t KB = K / 16;
+  c.nt = kThreads;
+  c.cols = 16;
   c.cg = KB >= 96 ? 8 : (KB >= 16 ? 16 : 32);
-  const int64_t KS = kThreads / c.cg;
+  const int64_t KS = c.nt / c.cg;
   const int64_t min_blocks = KB / KS;
   if (min_blocks < 1) return c;
-  const int nv = scale8 ? 8 : 7;
   for (int s = (c.cg == 32 ? 2 : 4); s >= 2; --s) {
     if (min_blocks < s - 1) continue;
-    const size_t smem = (size_t)kLutBytes + (size_t)s * nv * kThreads * 16 +
-                        (size_t)kWarps * kMaxTok * c.cg * 16 * 4 + (size_t)2 * kMaxTok * K * 2;
+    const size_t smem = gemv_smem(c.nt, c.cols, c.cg, s, scale8, K);
     if (smem <= 227 * 1024) {
       c.stages = s;
       c.smem = smem;
@@ -631,34 +664,34 @@ GemvCfg pick_cfg(int64_t K, bool scale8) {
   return c;
 }
 
-template <int CG, int S, bool kScale8, bool kSilu>
+template <int NT, int COLS, int CG, int S, bool kScale8, bool kSilu>
 int launch_gemv_t(const GemvArgs& g, int64_t grid, size_t smem, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(sparse_gemv_kernel<CG, S, kScale8, kSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             227 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(sparse_gemv_kernel<NT, COLS, CG, S, kScale8, kSilu>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
     attr_set[dev] = true;
   }
-  sparse_gemv_kernel<CG, S, kScale8, kSilu><<<(unsigned)grid, kThreads, smem, st>>>(g);
+  sparse_gemv_kernel<NT, COLS, CG, S, kScale8, kSilu><<<(unsigned)grid, NT, smem, st>>>(g);
   return B200FP4_STATUS_SUCCESS;
 }
 
 template <bool kScale8, bool kSilu>
 int launch_gemv(const GemvArgs& g, const GemvCfg& c, int64_t grid, cudaStream_t st) {
-  if (c.cg == 32) return launch_gemv_t<32, 2, kScale8, kSilu>(g, grid, c.smem, st);
+  if (c.cg == 32) return launch_gemv_t<256, 16, 32, 2, kScale8, kSilu>(g, grid, c.smem, st);
   if (c.cg == 8) {
-    if (c.stages == 4) return launch_gemv_t<8, 4, kScale8, kSilu>(g, grid, c.smem, st);
-    if (c.stages == 3) return launch_gemv_t<8, 3, kScale8, kSilu>(g, grid, c.smem, st);
-    return launch_gemv_t<8, 2, kScale8, kSilu>(g, grid, c.smem, st);
+    if (c.stages == 4) return launch_gemv_t<256, 16, 8, 4, kScale8, kSilu>(g, grid, c.smem, st);
+    if (c.stages == 3) return launch_gemv_t<256, 16, 8, 3, kScale8, kSilu>(g, grid, c.smem, st);
+    return launch_gemv_t<256, 16, 8, 2, kScale8, kSilu>(g, grid, c.smem, st);
   }
-  if (c.stages == 4) return launch_gemv_t<16, 4, kScale8, kSilu>(g, grid, c.smem, st);
-  if (c.stages == 3) return launch_gemv_t<16, 3, kScale8, kSilu>(g, grid, c.smem, st);
-  return launch_gemv_t<16, 2, kScale8, kSilu>(g, grid, c.smem, st);
+  if (c.stages == 4) return launch_gemv_t<256, 16, 16, 4, kScale8, kSilu>(g, grid, c.smem, st);
+  if (c.stages == 3) return launch_gemv_t<256, 16, 16, 3, kScale8, kSilu>(g, grid, c.smem, st);
+  return launch_gemv_t<256, 16, 16, 2, kScale8, kSilu>(g, grid, c.smem, st);
 }
 
 bool vector_ok(int64_t N, int64_t K, int64_t G, const SparseWeights& w, const void* A, int64_t lda) {
@@ -717,7 +750,7 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
   const bool s8 = (G == K / 8);
   const GemvCfg c = pick_cfg(K, s8);
   if (!c.ok) return B200FP4_STATUS_NOT_SUPPORTED;
-  const int slab = c.cg * 16;
+  const int slab = c.cg * c.cols;
   g.n_slabs = inter_silu > 0 ? (inter_silu + slab / 2 - 1) / (slab / 2) : (int)((N + slab - 1) / slab);
   int64_t grid = max_passes(P, E) * g.n_slabs;
   if (grid > (int64_t)sm_count()) grid = sm_count();
