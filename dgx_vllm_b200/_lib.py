@@ -40,6 +40,11 @@ SIGNATURES = {
     "b200fp4_dense_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_sparse_packed_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_fused_moe_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200fp4_ep_record_bytes": (_sz, [_i64, _i64]),
+    "b200fp4_ep_pack": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "b200fp4_fused_sparse_moe_records": (_i32, [_vp, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
+                                                _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_ep_combine": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_fused_moe_profile_events": (None, [_vp, _vp, _vp]),
     "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                         _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),

@@ -75,11 +75,13 @@ struct GemvArgs {
 __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
                     Plan plan, const __nv_bfloat16* __restrict__ conv_src, __half* __restrict__ conv_dst,
-                    int64_t conv_chunks) {
+                    int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks) {
   if (blockIdx.x > 0) {
     const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
     for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
-      const uint4 raw = reinterpret_cast<const uint4*>(conv_src)[i];
+      // rows of the source may be strided (conv_ld_chunks 16-byte chunks apart); the copy is dense
+      const int64_t row = i / conv_row_chunks, col = i - row * conv_row_chunks;
+      const uint4 raw = reinterpret_cast<const uint4*>(conv_src)[row * conv_ld_chunks + col];
       const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
       __half2 h[4];
 #pragma unroll
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(kPlanThreads)
   for (int e = tid; e < E; e += kPlanThreads) s_count[e] = 0;
   __syncthreads();
   for (int p = tid; p < P; p += kPlanThreads) {
-    int e = ids[p];
+    int e = ids[(int64_t)(p / ids_topk) * ids_ld + (p % ids_topk)];   // ids rows may be strided
     if (expert_map != nullptr) e = (e >= 0 && e < global_E) ? expert_map[e] : -1;
     if (e < 0 || e >= E) e = -1;
     plan.mapped[p] = e;
@@ -588,7 +590,7 @@ __global__ void generic_gemv_kernel(SparseWeights w, int mode, const void* A, in
 // out[m, h] = sum_t weight(m,t) * down[m*topk + t, h] over pairs whose expert is local.
 __global__ void weighted_reduce_kernel(const float* __restrict__ down, const float* __restrict__ topk_w,
                                        const int* __restrict__ mapped, void* out, int out_dtype, int M, int topk, int H,
-                                       int unweighted) {
+                                       int unweighted, int64_t ld_w) {
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   const int m = blockIdx.y;
   if (h >= H || m >= M) return;
@@ -597,7 +599,7 @@ __global__ void weighted_reduce_kernel(const float* __restrict__ down, const flo
     const int p = m * topk + t;
     if (mapped[p] < 0) continue;
     const float v = down[(int64_t)p * H + h];
-    acc += unweighted ? v : v * topk_w[p];
+    acc += unweighted ? v : v * topk_w[(int64_t)m * ld_w + t];
   }
   store_out(out, out_dtype, (int64_t)m * H + h, acc);
 }
@@ -717,18 +719,20 @@ int check_common(const void* A, int a_dtype, const void* out, int out_dtype, int
 }
 
 // Plan + (for bf16 activations) conversion to fp16 in one launch.
-void launch_plan(const int32_t* ids, int64_t P, const int32_t* expert_map, int64_t global_E, int64_t E,
-                 const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_elems, cudaStream_t st) {
+void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld, const int32_t* expert_map,
+                 int64_t global_E, int64_t E, const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_rows,
+                 int64_t a_cols, int64_t a_ld, cudaStream_t st) {
   int64_t chunks = 0;
   unsigned blocks = 1;
   if (a_bf16 != nullptr) {
-    chunks = a_elems / 8;
+    chunks = a_rows * a_cols / 8;
     int64_t nb = (chunks + kPlanThreads - 1) / kPlanThreads;
     if (nb > 2 * (int64_t)sm_count()) nb = 2 * (int64_t)sm_count();
     blocks += (unsigned)(nb < 1 ? 1 : nb);
   }
   moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan,
-                                                   reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks);
+                                                   reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks,
+                                                   (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8);
 }
 
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
@@ -773,7 +777,7 @@ int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, con
       return B200FP4_STATUS_ALLOC_FAILED;
     Plan plan = carve_plan(workspace, P, E);
     __half* a16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + align_up(plan_bytes(P, E), 256));
-    launch_plan(expert_ids, P, nullptr, 0, E, plan, a_bf16 ? A : nullptr, a16, P * K, st);
+    launch_plan(expert_ids, P, 1, 1, nullptr, 0, E, plan, a_bf16 ? A : nullptr, a16, P, K, K, st);
     zero_unmapped_rows_kernel<<<(unsigned)P, 128, 0, st>>>(plan.mapped, (int)P, out, out_dtype, N, (int)N);
     rc = run_projection(w, plan, a_bf16 ? a16 : reinterpret_cast<const __half*>(A), K, 1, out, out_dtype, N, P, N, K,
                         G, E, 0, st);
@@ -932,15 +936,16 @@ extern "C" size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int
          align_up((size_t)P * I * sizeof(__half), 256) + align_up((size_t)P * H * sizeof(float), 256);
 }
 
-extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const float* topk_weights,
-                                        const int32_t* topk_ids, const int32_t* expert_map, int64_t global_E,
-                                        const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
-                                        const float* w13_g, int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta,
-                                        const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out, int out_dtype,
-                                        int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
-                                        int apply_router_weight_on_input, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
+// ld_h / ld_w / ld_ids: row strides (in elements) of hidden, topk_weights and topk_ids.
+static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const float* topk_weights, int64_t ld_w,
+                          const int32_t* topk_ids, int64_t ld_ids, const int32_t* expert_map, int64_t global_E,
+                          const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
+                          int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
+                          const float* w2_g, int64_t G2, void* out, int out_dtype, int64_t M, int64_t topk, int64_t H,
+                          int64_t I, int64_t E, int apply_router_weight_on_input, void* workspace, size_t workspace_bytes,
+                          void* stream) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (ld_h < H || ld_w < topk || ld_ids < topk || (ld_h % 8) != 0) return B200FP4_STATUS_INVALID_VALUE;
   const int64_t P = M * topk;
   int rc = check_common(hidden, h_dtype, out, out_dtype, P, 2 * I, H, G13, E);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
@@ -960,7 +965,7 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
   w2.comp_e = (I / 4) * H; w2.comp_pair = 2 * H; w2.comp_odd = H;
   w2.meta_e = (I / 8) * H; w2.meta_row = H; w2.scale_e = G2 * H; w2.scale_row = H;
   // the fused layer only exists in vectorised form
-  if (I % 16 != 0 || !vector_ok(2 * I, H, G13, w13, hidden, H) || !vector_ok(H, I, G2, w2, hidden, I))
+  if (I % 16 != 0 || !vector_ok(2 * I, H, G13, w13, hidden, ld_h) || !vector_ok(H, I, G2, w2, hidden, I))
     return B200FP4_STATUS_NOT_SUPPORTED;
   if (!workspace || !aligned(workspace, 256) || workspace_bytes < b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E))
     return B200FP4_STATUS_ALLOC_FAILED;
@@ -975,9 +980,9 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
   float* down = reinterpret_cast<float*>(ws + off);
   const bool bf = h_dtype == B200FP4_DTYPE_BF16;
 
-  launch_plan(topk_ids, P, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M * H, st);
+  launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M, H, ld_h, st);
   if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
-  rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), H, (int)topk, act,
+  rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk, act,
                       B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
@@ -986,6 +991,114 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
   if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);
   weighted_reduce_kernel<<<grid, 256, 0, st>>>(down, topk_weights, plan.mapped, out, out_dtype, (int)M, (int)topk,
-                                               (int)H, apply_router_weight_on_input ? 1 : 0);
+                                               (int)H, apply_router_weight_on_input ? 1 : 0, ld_w);
   return finish_launch(4);
+}
+
+extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const float* topk_weights,
+                                        const int32_t* topk_ids, const int32_t* expert_map, int64_t global_E,
+                                        const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
+                                        const float* w13_g, int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta,
+                                        const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out, int out_dtype,
+                                        int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
+                                        int apply_router_weight_on_input, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  return fused_moe_impl(hidden, H, h_dtype, topk_weights, topk, topk_ids, topk, expert_map, global_E, w13_comp, w13_meta,
+                        w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out, out_dtype, M, topk, H, I, E,
+                        apply_router_weight_on_input, workspace, workspace_bytes, stream);
+}
+
+// ------------------------------------------------------------------------------------------ expert parallel
+
+// One record per token: [H activations (16-bit) | topk expert ids (i32) | topk router weights (f32)].
+extern "C" size_t b200fp4_ep_record_bytes(int64_t H, int64_t topk) {
+  if (H <= 0 || topk <= 0) return 0;
+  return align_up((size_t)H * 2 + (size_t)topk * 8, 16);
+}
+
+namespace b200fp4 {
+namespace {
+// out[g][b] = record of token b, for every destination rank g (fixed-capacity dispatch slots)
+__global__ void ep_pack_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ ids,
+                               const float* __restrict__ w, int B, int H, int topk, int G, int64_t rec_chunks,
+                               uint4* __restrict__ out) {
+  const int b = blockIdx.x;
+  const int h_chunks = H / 8;
+  __shared__ uint4 s_tail[64];
+  const int tail_chunks = (int)rec_chunks - h_chunks;
+  if (threadIdx.x < tail_chunks * 4) {
+    const int i = threadIdx.x;            // 32-bit word index inside the tail: ids first, then weights
+    uint32_t v = 0;
+    if (i < topk) v = (uint32_t)ids[(int64_t)b * topk + i];
+    else if (i < 2 * topk) v = __float_as_uint(w[(int64_t)b * topk + i - topk]);
+    reinterpret_cast<uint32_t*>(s_tail)[i] = v;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < rec_chunks; c += blockDim.x) {
+    const uint4 v = c < h_chunks ? hidden[(int64_t)b * h_chunks + c] : s_tail[c - h_chunks];
+    for (int g = 0; g < G; ++g) out[((int64_t)g * B + b) * rec_chunks + c] = v;
+  }
+}
+
+// out[b, :] = sum over ranks g of parts[g][b, :] accumulated in fp32
+template <typename T>
+__global__ void ep_combine_kernel(const T* __restrict__ parts, int B, int H, int G, T* __restrict__ out) {
+  const int64_t n = (int64_t)B * H;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2; i < n; i += (int64_t)gridDim.x * blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int g = 0; g < G; ++g) {
+      a0 += to_f32<T>(parts[(int64_t)g * n + i]);
+      a1 += to_f32<T>(parts[(int64_t)g * n + i + 1]);
+    }
+    out[i] = from_f32<T>(a0);
+    out[i + 1] = from_f32<T>(a1);
+  }
+}
+}  // namespace
+}  // namespace b200fp4
+
+extern "C" int b200fp4_ep_pack(const void* hidden, const int32_t* topk_ids, const float* topk_weights, int64_t B,
+                               int64_t H, int64_t topk, int64_t G, void* records, void* stream) {
+  if (B < 0 || H <= 0 || (H % 8) != 0 || topk <= 0 || topk > 64 || G <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (B == 0) return B200FP4_STATUS_SUCCESS;
+  if (!hidden || !topk_ids || !topk_weights || !records || !aligned(hidden, 16) || !aligned(records, 16))
+    return B200FP4_STATUS_INVALID_VALUE;
+  const int64_t rec_chunks = (int64_t)b200fp4_ep_record_bytes(H, topk) / 16;
+  ep_pack_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint4*>(hidden), topk_ids,
+                                                               topk_weights, (int)B, (int)H, (int)topk, (int)G,
+                                                               rec_chunks, reinterpret_cast<uint4*>(records));
+  return finish_launch(1);
+}
+
+extern "C" int b200fp4_ep_combine(const void* parts, int dtype, int64_t B, int64_t H, int64_t G, void* out, void* stream) {
+  if (B < 0 || H <= 0 || (H % 2) != 0 || G <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (dtype != B200FP4_DTYPE_BF16 && dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (B == 0) return B200FP4_STATUS_SUCCESS;
+  if (!parts || !out) return B200FP4_STATUS_INVALID_VALUE;
+  int64_t blocks = (B * H / 2 + 255) / 256;
+  if (blocks > 4 * (int64_t)sm_count()) blocks = 4 * (int64_t)sm_count();
+  if (dtype == B200FP4_DTYPE_BF16)
+    ep_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(parts), (int)B, (int)H, (int)G, reinterpret_cast<__nv_bfloat16*>(out));
+  else
+    ep_combine_kernel<__half><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const __half*>(parts), (int)B, (int)H, (int)G, reinterpret_cast<__half*>(out));
+  return finish_launch(1);
+}
+
+// The fused layer over received dispatch records ([T] records of record_bytes each, as written by
+// b200fp4_ep_pack on the source ranks): activations, ids and weights are read in place.
+extern "C" int b200fp4_fused_sparse_moe_records(const void* records, int64_t record_bytes, int h_dtype,
+                                                const int32_t* expert_map, int64_t global_E, const uint8_t* w13_comp,
+                                                const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
+                                                int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta,
+                                                const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out,
+                                                int out_dtype, int64_t T, int64_t topk, int64_t H, int64_t I, int64_t E,
+                                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!records || record_bytes != (int64_t)b200fp4_ep_record_bytes(H, topk)) return B200FP4_STATUS_INVALID_VALUE;
+  const unsigned char* r = reinterpret_cast<const unsigned char*>(records);
+  return fused_moe_impl(r, record_bytes / 2, h_dtype, reinterpret_cast<const float*>(r + H * 2 + topk * 4),
+                        record_bytes / 4, reinterpret_cast<const int32_t*>(r + H * 2), record_bytes / 4, expert_map,
+                        global_E, w13_comp, w13_meta, w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out,
+                        out_dtype, T, topk, H, I, E, 0, workspace, workspace_bytes, stream);
 }

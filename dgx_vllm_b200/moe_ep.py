@@ -48,10 +48,12 @@ def unpack_records(rec: torch.Tensor, H: int, topk: int, dtype: torch.dtype):
 class ExpertParallelMoE:
     """One MoE layer sharded over the ranks of `group`.
 
-    local_moe_fn(hidden [T,H], topk_w [T,topk] f32, topk_ids [T,topk] i32 (global ids),
-                 expert_map [global_E] i32) -> [T,H]
-    computes the contribution of this rank's experts; by default it is the CUDA fused op over
-    `w13` / `w2` (dicts with comp_T, meta_T, scale_T, g_scales for the local experts)."""
+    With CUDA tensors the step is: ep_pack kernel -> all_to_all -> fused sparse MoE reading the
+    received records in place -> all_to_all -> ep_combine kernel (7 launches + 2 collectives).
+
+    `local_moe_fn(hidden [T,H], topk_w [T,topk] f32, topk_ids [T,topk] i32 (global ids),
+    expert_map [global_E] i32) -> [T,H]`, when given, replaces the CUDA ops and the torch
+    packing path is used instead (this is how the dispatch/combine logic is tested on CPU ranks)."""
 
     def __init__(self, global_E: int, inter: int, w13: Optional[dict], w2: Optional[dict], group=None,
                  local_moe_fn: Optional[Callable] = None):
@@ -64,7 +66,8 @@ class ExpertParallelMoE:
         self.inter = inter
         self.w13, self.w2 = w13, w2
         self._emap = None
-        self._fn = local_moe_fn or self._cuda_local
+        self._fn = local_moe_fn
+        self._bufs = {}
 
     def _cuda_local(self, hidden, topk_w, topk_ids, emap):
         from . import sparse_fp4_v7 as sp7
@@ -77,12 +80,9 @@ class ExpertParallelMoE:
             self._emap = expert_map_for_rank(self.global_E, self.world, self.rank, device)
         return self._emap
 
-    def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+    def _forward_torch(self, hidden, topk_w, topk_ids, emap):
         B, H = hidden.shape
         topk = topk_ids.shape[1]
-        emap = self.expert_map(hidden.device)
-        if self.world == 1:
-            return self._fn(hidden, topk_w, topk_ids, emap)
         G = self.world
         rec = pack_records(hidden, topk_w, topk_ids)                       # [B, R]
         send = rec.unsqueeze(0).expand(G, B, rec.shape[1]).contiguous()    # one slot block per peer
@@ -93,3 +93,51 @@ class ExpertParallelMoE:
         back = torch.empty_like(part)
         dist.all_to_all_single(back, part.contiguous(), group=self.group)  # combine
         return back.view(G, B, H).float().sum(0).to(hidden.dtype)
+
+    def _forward_cuda(self, hidden, topk_w, topk_ids, emap):
+        from . import _lib
+        from ._torch_util import dtype_code, ptr, require, stream_ptr, workspace
+        dev = hidden.device
+        B, H = hidden.shape
+        topk = topk_ids.shape[1]
+        G = self.world
+        L = _lib.lib()
+        require(hidden.is_contiguous() and hidden.dtype in (torch.bfloat16, torch.float16), "hidden must be contiguous 16-bit")
+        ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        ids = ids.contiguous()
+        tw = topk_w if topk_w.dtype == torch.float32 else topk_w.float()
+        tw = tw.contiguous()
+        R = L.b200fp4_ep_record_bytes(H, topk)
+        key = (dev.index, B, H, topk, hidden.dtype)
+        bufs = self._bufs.get(key)
+        if bufs is None:
+            bufs = (torch.empty(G * B * R, dtype=torch.uint8, device=dev), torch.empty(G * B * R, dtype=torch.uint8, device=dev),
+                    torch.empty(G * B, H, dtype=hidden.dtype, device=dev), torch.empty(G * B, H, dtype=hidden.dtype, device=dev))
+            self._bufs[key] = bufs
+        send, recv, part, back = bufs
+        T = G * B
+        E = self.global_E // G
+        k = ("comp_T", "meta_T", "scale_T", "g_scales")
+        ws = workspace(dev, L.b200fp4_fused_moe_workspace_bytes(T, topk, H, self.inter, E))
+        out = torch.empty(B, H, dtype=hidden.dtype, device=dev)
+        code = dtype_code(hidden.dtype)
+        with torch.cuda.device(dev):
+            _lib.check(L.b200fp4_ep_pack(ptr(hidden), ptr(ids), ptr(tw), B, H, topk, G, ptr(send), stream_ptr(dev)), "ep_pack")
+            dist.all_to_all_single(recv, send, group=self.group)                                   # dispatch
+            _lib.check(L.b200fp4_fused_sparse_moe_records(
+                ptr(recv), R, code, ptr(emap), emap.numel(),
+                *[ptr(self.w13[x]) for x in k], self.w13["scale_T"].shape[1],
+                *[ptr(self.w2[x]) for x in k], self.w2["scale_T"].shape[1],
+                ptr(part), code, T, topk, H, self.inter, E, ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_records")
+            dist.all_to_all_single(back, part, group=self.group)                                   # combine
+            _lib.check(L.b200fp4_ep_combine(ptr(back), code, B, H, G, ptr(out), stream_ptr(dev)), "ep_combine")
+        return out
+
+    def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        emap = self.expert_map(hidden.device)
+        if self.world == 1:
+            fn = self._fn or self._cuda_local
+            return fn(hidden, topk_w, topk_ids, emap)
+        if self._fn is not None:
+            return self._forward_torch(hidden, topk_w, topk_ids, emap)
+        return self._forward_cuda(hidden, topk_w, topk_ids, emap)

@@ -241,6 +241,29 @@ B200FP4_API int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, 
                                              const float* topk_weights, int64_t M, int64_t topk,
                                              int64_t H, void* out, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert-parallel helpers (no counterpart in the reference, which has no multi-GPU code of its
+ * own: it serves with tensor parallelism through vLLM, entrypoint.sh:100-116).  A dispatch record
+ * is [H activations (16-bit) | topk ids (i32) | topk router weights (f32)], padded to 16 bytes.
+ *   b200fp4_ep_pack       writes records[g][b] for every destination rank g (send buffer of the
+ *                         fixed-capacity all-to-all)
+ *   b200fp4_fused_sparse_moe_records   b200fp4_fused_sparse_moe over T received records read in
+ *                         place (router weights always applied to the output)
+ *   b200fp4_ep_combine    out[b] = sum_g parts[g][b] in fp32 (partial rows returned by the ranks)
+ * ------------------------------------------------------------------------------------------- */
+B200FP4_API size_t b200fp4_ep_record_bytes(int64_t H, int64_t topk);
+B200FP4_API int b200fp4_ep_pack(const void* hidden, const int32_t* topk_ids, const float* topk_weights,
+                                int64_t B, int64_t H, int64_t topk, int64_t G, void* records,
+                                void* stream);
+B200FP4_API int b200fp4_fused_sparse_moe_records(
+    const void* records, int64_t record_bytes, int h_dtype, const int32_t* expert_map, int64_t global_E,
+    const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
+    int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
+    const float* w2_g, int64_t G2, void* out, int out_dtype, int64_t T, int64_t topk, int64_t H,
+    int64_t I, int64_t E, void* workspace, size_t workspace_bytes, void* stream);
+B200FP4_API int b200fp4_ep_combine(const void* parts, int dtype, int64_t B, int64_t H, int64_t G,
+                                   void* out, void* stream);
+
 /* Benchmark hook (no counterpart in the reference): when the three cudaEvent_t handles are non-NULL,
  * b200fp4_fused_sparse_moe records them on its stream before the gate_up GEMV, between the two
  * GEMVs and after the down GEMV, so a caller can time the two dominant kernels inside a fused

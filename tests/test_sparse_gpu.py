@@ -138,3 +138,52 @@ def test_argument_validation():
         sp7.batched_sparse_v7(A.cuda().float(), *_cuda(comp, meta, scale, g, ids))   # wrong dtype
     with pytest.raises(RuntimeError):
         sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta[:, :4], scale, g, ids))    # wrong meta shape
+
+
+def test_ep_records_pack_fused_combine_single_gpu():
+    # the expert-parallel kernels without the collectives: two "ranks" emulated on one GPU by
+    # swapping the record blocks by hand (what the all-to-all does), against the full-layer oracle
+    from dgx_vllm_b200 import _lib, synth
+    from dgx_vllm_b200._torch_util import workspace
+    L = _lib.lib()
+    G, E_glob, H, I, B, topk = 2, 8, 256, 128, 5, 3
+    E = E_glob // G
+    w13 = synth.make_sparse_experts(E_glob, 2 * I, H, 31, "cpu", oracle_quantize_fn)
+    w2 = synth.make_sparse_experts(E_glob, H, I, 32, "cpu", oracle_quantize_fn)
+    keys = ("comp_T", "meta_T", "scale_T", "g_scales")
+    R = L.b200fp4_ep_record_bytes(H, topk)
+    assert R % 16 == 0 and R >= H * 2 + topk * 8
+    hid, tws, idss, sends = [], [], [], []
+    for r in range(G):
+        tw, ids = synth.make_routing(B, E_glob, topk, 40 + r, "cpu")
+        h = synth.make_hidden(B, H, 50 + r, "cpu")
+        send = torch.empty(G * B * R, dtype=torch.uint8, device="cuda")
+        hc, ic, wc = h.cuda(), ids.cuda(), tw.cuda()
+        _lib.check(L.b200fp4_ep_pack(hc.data_ptr(), ic.data_ptr(), wc.data_ptr(), B, H, topk, G, send.data_ptr(), 0), "pack")
+        hid.append(h), tws.append(tw), idss.append(ids), sends.append(send.view(G, B * R))
+    torch.cuda.synchronize()
+    parts = []
+    for r in range(G):                                        # rank r receives block r of every sender
+        recv = torch.cat([sends[src][r] for src in range(G)]).contiguous()
+        emap = torch.full((E_glob,), -1, dtype=torch.int32)
+        emap[r * E:(r + 1) * E] = torch.arange(E, dtype=torch.int32)
+        loc13 = [w13[k][r * E:(r + 1) * E].contiguous().cuda() for k in keys]
+        loc2 = [w2[k][r * E:(r + 1) * E].contiguous().cuda() for k in keys]
+        part = torch.empty(G * B, H, dtype=torch.bfloat16, device="cuda")
+        ws = workspace(torch.device("cuda", 0), L.b200fp4_fused_moe_workspace_bytes(G * B, topk, H, I, E))
+        emc = emap.cuda()
+        _lib.check(L.b200fp4_fused_sparse_moe_records(recv.data_ptr(), R, _lib.BF16, emc.data_ptr(), E_glob,
+                                                      *[t.data_ptr() for t in loc13], loc13[2].shape[1],
+                                                      *[t.data_ptr() for t in loc2], loc2[2].shape[1],
+                                                      part.data_ptr(), _lib.BF16, G * B, topk, H, I, E, ws.data_ptr(), ws.numel(), 0), "records")
+        torch.cuda.synchronize()
+        parts.append(part.view(G, B, H))
+    for src in range(G):                                      # combine: rank src gets its block back from every rank
+        back = torch.stack([parts[r][src] for r in range(G)]).contiguous()
+        out = torch.empty(B, H, dtype=torch.bfloat16, device="cuda")
+        _lib.check(L.b200fp4_ep_combine(back.data_ptr(), _lib.BF16, B, H, G, out.data_ptr(), 0), "combine")
+        torch.cuda.synchronize()
+        n = lambda d: tuple(d[k].numpy() for k in keys)
+        ref = oracle.fused_sparse_moe(hid[src].float().numpy(), tws[src].numpy(), idss[src].numpy(), None, n(w13), n(w2), I,
+                                      round_fp16=False)
+        assert rel_err(to_np(out), ref) < 2e-2                # partial rows travel as bf16
