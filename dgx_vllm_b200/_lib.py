@@ -39,6 +39,7 @@ SIGNATURES = {
     "b200fp4_sparse_gemv_static": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp]),
     "b200fp4_dense_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_sparse_packed_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_convert_to_sparse_2of4": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "b200fp4_fused_moe_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "b200fp4_ep_record_bytes": (_sz, [_i64, _i64]),
     "b200fp4_ep_pack": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),

@@ -169,3 +169,27 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
             ptr(out), dtype_code(out.dtype), M, topk, H, I, E, 1 if apply_router_weight_on_input else 0,
             ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_v7")
     return out
+
+
+def convert_weight_batch_to_v7(weights, scales, g_scales, device="cuda", batch_size=16):
+    """NVFP4 expert weights -> the 2:4 tensors the ops above take, on the GPU in two launches.
+
+    Mirrors convert_weight_batch_to_v7 (sparse_fp4_kernel/sparse_v7_moe_patch.py:96-129): weights
+    [E,N,K/2] uint8, scales [E,N,G] e4m3, g_scales [E] -> (comp_T [E,K/4,N], meta_T [E,K/8,N],
+    scale_T [E,G,N], g_scales f32 on the device).  batch_size is accepted for signature
+    compatibility.  Ties between equal magnitudes keep the lower index."""
+    dev = torch.device(device)
+    w = weights.to(dev).contiguous()
+    sc = scales.to(dev).contiguous()
+    require(w.dim() == 3 and w.dtype == torch.uint8, "weights must be [E,N,K/2] uint8")
+    require(sc.dim() == 3 and sc.shape[:2] == w.shape[:2], "scales must be [E,N,G]")
+    E, N, K2 = w.shape
+    K, G = K2 * 2, sc.shape[2]
+    require(K % 8 == 0, "K must be a multiple of 8")
+    comp_T = torch.empty((E, K // 4, N), dtype=torch.uint8, device=dev)
+    meta_T = torch.empty((E, K // 8, N), dtype=torch.uint8, device=dev)
+    scale_T = torch.empty((E, G, N), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200fp4_convert_to_sparse_2of4(ptr(w), ptr(sc), E, N, K, G, ptr(comp_T), ptr(meta_T),
+                                                            ptr(scale_T), stream_ptr(dev)), "convert_weight_batch_to_v7")
+    return comp_T, meta_T, scale_T, g_scales.float().to(dev)

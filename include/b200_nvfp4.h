@@ -174,6 +174,16 @@ B200FP4_API int b200fp4_sparse_packed_gemv(const void* A, int a_dtype, const uin
                                            int64_t E, void* workspace, size_t workspace_bytes,
                                            void* stream);
 
+/* Load-time converter: NVFP4 expert weights [E, N, K/2] (+ block scales [E, N, G]) -> the 2:4
+ * compressed, N-contiguous tensors above (comp_T [E,K/4,N], meta_T [E,K/8,N], scale_T [E,G,N]).
+ * Replaces unpack_fp4_nibbles / apply_2of4_sparsity_fast / convert_expert_to_v7_gpu /
+ * convert_weight_batch_to_v7, sparse_fp4_kernel/sparse_v7_moe_patch.py:39-129.  Per group of four the
+ * two largest magnitudes are kept, ties resolved towards the lower index (the reference's
+ * torch.topk leaves ties unspecified), indices stored ascending.  scales / scale_T may both be NULL. */
+B200FP4_API int b200fp4_convert_to_sparse_2of4(const uint8_t* codes, const uint8_t* scales, int64_t E,
+                                               int64_t N, int64_t K, int64_t G, uint8_t* comp_T,
+                                               uint8_t* meta_T, uint8_t* scale_T, void* stream);
+
 /* fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map, w13_*, w2_*, inter_size,
  * apply_router_weight_on_input), sparse_fp4_v7.cu:607-742: gate_up GEMV -> SiLU(gate)*up ->
  * down GEMV -> router-weighted sum per token.

@@ -117,3 +117,18 @@ def test_prefill_config_m4096_sampled_rows_and_linearity():
     assert rel_err(to_np(out[torch.from_numpy(rows).cuda()]), ref) < TOL
     out2 = cutlass_scaled_fp4_mm(xc, wc, xs, ws, a1 * 2, torch.bfloat16)
     assert torch.equal(out2.float(), out.float() * 2)
+
+
+def test_torch_custom_ops_dispatch_to_the_library():
+    import dgx_vllm_b200.torch_ops  # noqa: F401
+    x, w = _rand(32, 128, 256, 9)
+    gx, gw = float(oracle.global_scale(x.float().numpy())), float(oracle.global_scale(w.float().numpy()))
+    g = lambda v: torch.tensor([v], dtype=torch.float32, device="cuda")
+    xc, xs = torch.ops.b200_nvfp4.scaled_fp4_quant(x.cuda(), g(gx), True)
+    wc, ws = torch.ops.b200_nvfp4.scaled_fp4_quant(w.cuda(), g(gw), True)
+    out = torch.empty(32, 128, dtype=torch.bfloat16, device="cuda")
+    torch.ops.b200_nvfp4.cutlass_scaled_fp4_mm(out, xc, wc, xs, ws, g(1.0 / (gx * gw)))
+    oc, osf = oracle.quantize_bf16(bf16_bits(x), gx)
+    wq, wsf = oracle.quantize_bf16(bf16_bits(w), gw)
+    ref = oracle.matmul_nt(oracle.dequantize(oc, osf, gx), oracle.dequantize(wq, wsf, gw))
+    assert rel_err(to_np(out), ref) < TOL

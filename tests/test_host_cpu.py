@@ -134,3 +134,15 @@ def test_expert_parallel_dispatch_combine_gloo_world2(tmp_path):
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
+def test_torch_custom_ops_registered_with_fake_impls():
+    import dgx_vllm_b200.torch_ops  # noqa: F401
+    ns = torch.ops.b200_nvfp4
+    for name in ("scaled_fp4_quant", "cutlass_scaled_fp4_mm", "cutlass_fp4_group_mm", "batched_sparse_v7", "fused_sparse_moe_v7"):
+        assert hasattr(ns, name)
+    x = torch.empty(200, 4096, dtype=torch.bfloat16, device="meta")
+    codes, sf = ns.scaled_fp4_quant(x, torch.empty(1, device="meta"), True)
+    assert tuple(codes.shape) == (200, 2048) and tuple(sf.shape) == (256, 256) and sf.dtype == torch.float8_e4m3fn
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ns.scaled_fp4_quant(torch.zeros(4, 16, dtype=torch.bfloat16), torch.ones(1), True)     # no CPU kernel

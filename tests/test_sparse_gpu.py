@@ -187,3 +187,29 @@ def test_ep_records_pack_fused_combine_single_gpu():
         ref = oracle.fused_sparse_moe(hid[src].float().numpy(), tws[src].numpy(), idss[src].numpy(), None, n(w13), n(w2), I,
                                       round_fp16=False)
         assert rel_err(to_np(out), ref) < 2e-2                # partial rows travel as bf16
+
+
+def test_convert_weight_batch_to_v7_matches_oracle_and_reference_golden(golden_dir):
+    import os
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    rng = np.random.default_rng(5)
+    E, N, K = 3, 80, 96
+    codes = rng.integers(0, 256, (E, N, K // 2), dtype=np.uint8)
+    sf = rng.integers(0, 127, (E, N, K // 16), dtype=np.uint8)
+    comp, meta, scale, g = sp7.convert_weight_batch_to_v7(torch.from_numpy(codes), torch.from_numpy(sf), torch.ones(E))
+    for e in range(E):
+        oc, om = oracle.sparse_2of4_pack(codes[e])                 # bit-exact, ties included (same rule)
+        np.testing.assert_array_equal(to_np(comp[e]), oc)
+        np.testing.assert_array_equal(to_np(meta[e]), om)
+        np.testing.assert_array_equal(to_np(scale[e]), sf[e].T)
+    # the reference's own converter output (golden): identical wherever the top-2 choice is unambiguous
+    gd = np.load(os.path.join(golden_dir, "sparse_convert.npz"))
+    comp, meta, scale, _ = sp7.convert_weight_batch_to_v7(torch.from_numpy(gd["codes"][None]), torch.from_numpy(gd["sf"][None]),
+                                                         torch.ones(1))
+    nib = gd["nibbles"]
+    Nn, Kk = nib.shape
+    mag = np.abs(oracle.E2M1_LUT[nib]).reshape(Nn, Kk // 4, 4)
+    srt = np.sort(mag, axis=2)
+    tie_free = (srt[:, :, 1] != srt[:, :, 2]).T
+    np.testing.assert_array_equal(to_np(comp[0])[tie_free], gd["comp_T"][tie_free])
+    np.testing.assert_array_equal(to_np(scale[0]), gd["scale_T"])
