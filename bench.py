@@ -234,6 +234,145 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
     return parts
 
 
+def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
+    """BASELINE configs[3]: 8192 tokens x hidden 2048, 512 experts, Zipf(1.1)-skewed top-10 routing,
+    dense NVFP4 experts (gate_up 1024x2048, down 2048x512) through the grouped path: permute ->
+    per-expert quantize -> grouped GEMM -> SiLU*up + quantize -> grouped GEMM -> combine."""
+    import torch
+    from dgx_vllm_b200 import grouped_moe as gm
+    from dgx_vllm_b200 import scaled_fp4_quant, synth
+    from dgx_vllm_b200.ops import last_gemm_status
+
+    T, E, H, I, topk = 8192, 512, 2048, 512, 10
+    gen = torch.Generator(device=dev).manual_seed(11)
+
+    def experts(N, K):
+        codes = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty(E, (N + 127) // 128 * 128, (K // 16 + 3) // 4 * 4, dtype=torch.uint8, device=dev)
+        gs = torch.empty(E, dtype=torch.float32, device=dev)
+        for e0 in range(0, E, 64):
+            w = (0.02 * torch.randn(64, N, K, generator=gen, device=dev)).to(torch.bfloat16)
+            for i in range(64):
+                g = synth.global_scale_of(w[i])
+                c, s_ = scaled_fp4_quant(w[i], g)
+                codes[e0 + i], sf[e0 + i], gs[e0 + i] = c, s_.view(torch.uint8), g[0]
+        return codes, sf, gs
+
+    w13c, w13s, w13g = experts(2 * I, H)
+    w2c, w2s, w2g = experts(H, I)
+    hidden = synth.make_hidden(T, H, 5, dev)
+    tw, ids = synth.make_routing(T, E, topk, 6, dev, zipf=1.1)
+    a1 = (448.0 * 6.0 / hidden.float().abs().max()).repeat(E).float()
+    a2 = torch.full((E,), 448.0 * 6.0 / 2.0, dtype=torch.float32, device=dev)
+
+    def run():
+        return gm.nvfp4_moe_prefill(hidden, tw, ids, w13c, w13s, w13g, w2c, w2s, w2g, a1, a2)
+
+    for _ in range(3):
+        run()
+    status = last_gemm_status(dev)
+    ts = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        run()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e-3)
+    t = statistics.mean(ts)
+    flops = 2.0 * T * topk * (2 * I * H + H * I)
+    wbytes = E * (2 * I * H + H * I) * 0.5625
+    return {"tokens_per_s": T / t, "ms": t * 1e3, "tflops": flops / t / 1e12, "weight_GBps": wbytes / t / 1e9,
+            "frac_of_measured_hbm_weights_only": wbytes / t / 1e9 / hbm_peak, "gemm_status": status,
+            "config": "8192 tokens, 512 experts, Zipf(1.1) top-10, dense NVFP4 experts, grouped path, 9 launches"}
+
+
+def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_layers: int = 4, reps: int = 5):
+    """BASELINE configs[4]: Qwen3-Next-80B-A3B-shaped NVFP4 linear stack for decode -- 48 layers of
+    (512 routed 2:4-sparse experts, top-10) + 1 shared dense NVFP4 expert, mixers stubbed by a fixed
+    bf16 input per layer.  Captured once per batch size in a CUDA graph and replayed.
+    Weights: `distinct_layers` independent layer sets cycled over the 48 layers (each set is 704 MB of
+    routed weights, far beyond L2, and every layer uses its own routing)."""
+    import torch
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant, synth
+    from dgx_vllm_b200 import grouped_moe as gm
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+
+    E, H, I, topk = E_TOTAL, HIDDEN, INTER, TOPK
+    keys = ("comp_T", "meta_T", "scale_T", "g_scales")
+
+    def qfn(w, gs):
+        c, s_ = scaled_fp4_quant(w, gs, is_sf_swizzled_layout=False)
+        return c, s_.view(torch.uint8)
+
+    sets = []
+    gen = torch.Generator(device=dev).manual_seed(99)
+    for li in range(distinct_layers):
+        w13 = synth.make_sparse_experts(E, 2 * I, H, 3000 + li, dev, qfn)
+        w2 = synth.make_sparse_experts(E, H, I, 4000 + li, dev, qfn)
+        sh = []
+        for (N, K) in ((2 * I, H), (H, I)):
+            w = (0.02 * torch.randn(N, K, generator=gen, device=dev)).to(torch.bfloat16)
+            g = synth.global_scale_of(w)
+            c, s_ = scaled_fp4_quant(w, g)
+            sh.append((c, s_, g))
+        sets.append((w13, w2, sh))
+    emap = torch.empty(0, dtype=torch.int32, device=dev)
+    eo1 = lambda B: (torch.tensor([0, B], dtype=torch.int32, device=dev), torch.tensor([0, (B + 127) // 128 * 128], dtype=torch.int32, device=dev))
+    out = {}
+    for B in batches:
+        xs = [synth.make_hidden(B, H, 500 + l, dev) for l in range(layers)]
+        routes = [synth.make_routing(B, E, topk, 700 + l, dev) for l in range(layers)]
+        gx = torch.tensor([448.0 * 6.0 / 6.0], dtype=torch.float32, device=dev)
+        ga = torch.tensor([448.0 * 6.0 / 4.0], dtype=torch.float32, device=dev)
+        offs, bso = eo1(B)
+        alphas = [((1.0 / (gx * sh[0][2])).float(), (1.0 / (ga * sh[1][2])).float()) for (_, _, sh) in sets]
+
+        def stack():
+            acc = None
+            for l in range(layers):
+                w13, w2, sh = sets[l % distinct_layers]
+                x = xs[l]
+                tw, ids = routes[l]
+                y = sp7.fused_sparse_moe_v7(x, tw, ids, emap, *[w13[k] for k in keys], *[w2[k] for k in keys], I, False)
+                # shared expert: quant -> GEMM -> SiLU*up + quant -> GEMM
+                (c13, s13, g13), (c2, s2, g2) = sh
+                xc, xsf = scaled_fp4_quant(x, gx)
+                al13, al2 = alphas[l % distinct_layers]
+                gu = cutlass_scaled_fp4_mm(xc, c13, xsf, s13, al13, torch.bfloat16)
+                hc, hsf = gm.silu_and_mul_scaled_fp4_experts_quant(gu, ga, offs, bso)
+                z = cutlass_scaled_fp4_mm(hc, c2, hsf, s2, al2, torch.bfloat16)
+                acc = y + z if acc is None else acc + y + z
+            return acc
+
+        for _ in range(2):
+            stack()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            res = stack()
+        graph.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        t = statistics.mean(ts)
+        uniq = statistics.mean(int(r[1].unique().numel()) for r in routes)
+        byt = layers * (uniq * (BYTES_PER_EXPERT_GATE_UP + BYTES_PER_EXPERT_DOWN) + (2 * I * H + H * I) * 0.5625)
+        out[f"batch_{B}"] = {"tokens_per_s": B / t, "ms_per_token_step": t * 1e3, "us_per_layer": t / layers * 1e6,
+                             "weight_GBps": byt / t / 1e9, "finite": bool(torch.isfinite(res.float()).all().item())}
+        del graph
+    out["config"] = (f"{layers} layers, {distinct_layers} distinct weight sets cycled, routed 2:4 sparse experts + shared dense "
+                     f"NVFP4 expert per layer, one CUDA graph per batch size")
+    return out
+
+
 def config_dict(args):
     return {"workload": "sparse 2:4 NVFP4 MoE GEMV decode layer (BASELINE configs[2])", "experts": E_TOTAL,
             "hidden": HIDDEN, "moe_intermediate": INTER, "topk": TOPK, "batch_per_gpu": args.batch,
@@ -399,6 +538,10 @@ def main():
             del w13, w2, layer
             torch.cuda.empty_cache()
             line["parts"] = bench_dense_parts(dev, flush, hbm_peak)
+            torch.cuda.empty_cache()
+            line["parts"]["moe_prefill_8192_tokens"] = bench_moe_prefill(dev, flush, hbm_peak)
+            torch.cuda.empty_cache()
+            line["parts"]["decode_stack_48_layers"] = bench_decode_stack(dev)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(B)
         print(json.dumps(line), flush=True)
