@@ -19,17 +19,19 @@
 //     the global stores, so only the ~1200-cycle drain is exposed; it moves 25 % fewer bytes per flop.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code in the status word
 // and all roles drain out, so a protocol error cannot hang the GPU.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace b200fp4 {
+
+// CTA-pair (cta_group::2) kernel, gemm2.cu
+int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                     void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
+
 namespace {
 
 constexpr int kBM = 128;
 constexpr int kGemmThreads = 320;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale factors
 constexpr uint32_t kTmemCols = 512;
-constexpr long long kWaitCycles = 2000000000LL;   // ~1 s at 2 GHz
 
 struct GemmParams {
   const uint8_t* sfa;   // swizzled [ceil(M/128)*128, ceil(K/64)*4]
@@ -81,106 +83,6 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int
   return t;
 }
 
-// ---------------------------------------------------------------------------------------- PTX
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: returns false (and records `code`) if the phase does not complete in ~1 s.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) {
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// each lane writes 16 bytes (4 columns) of its own tensor-memory lane
-__device__ __forceinline__ void tcgen05_st_32x32_x4(uint32_t taddr, const uint4& v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptors (K-major).  Fields: start address >> 4 in bits [0,14), leading
-// byte offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in
-// [46,48), swizzle mode in [61,64) (2 = 128-byte, 4 = 64-byte, 6 = 32-byte swizzle).
-// Rows of kRowBytes (128, 64 or 32) bytes with the matching swizzle; 8-row atoms are 8*kRowBytes apart.
-template <int kRowBytes>
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-  constexpr uint64_t mode = kRowBytes == 128 ? 2ull : (kRowBytes == 64 ? 4ull : 6ull);
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)((8 * kRowBytes) >> 4) << 32) | (1ull << 46) |
-         (mode << 61);
-}
-
 // ---------------------------------------------------------------------------------------- kernel
 
 // BN = tile width; KB = 64-wide k-blocks (MMAs) per shared-memory stage.  Smaller stages do not change
@@ -221,7 +123,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* acc_full = bars + 2 * C::kStages;
   uint64_t* acc_empty = acc_full + C::kAcc;
   uint64_t* sf_ready = acc_empty + C::kAcc;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(sf_ready + C::kStages);
+  uint64_t* sf_full = sf_ready + C::kStages;     // scale factors of the stage have landed (before the operands)
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(sf_full + C::kStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = kGrouped ? p.g_hdr[0] : p.m_tiles;
@@ -231,11 +134,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
-      mbar_init(smem_u32(&sf_ready[s]), 128);
+      mbar_init(smem_u32(&sf_ready[s]), 4);       // one arrival per scale-factor warp
+      mbar_init(smem_u32(&sf_full[s]), 1);
     }
     for (int a = 0; a < C::kAcc; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 128);
+      mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -266,15 +170,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int kblocks = min(KB, KT - ks * KB);
           int sf_tiles = 0;
           for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((ti.sfb_tile0 + j) * 128 < p.N) ? 1 : 0;
-          const uint32_t bar = smem_u32(&full_bar[s]);
-          mbar_expect_tx(bar, (uint32_t)(C::kStageA + C::kStageB + kblocks * 512 * (1 + sf_tiles)));
-          tma_load_2d(smem_u32(st), &map_a, ks * C::kRowBytes, ti.a_row0, bar);
-          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
+          // the small scale-factor copies go first and on their own barrier, so the scale warps can
+          // move them into tensor memory while the operand tiles are still in flight
+          const uint32_t sbar = smem_u32(&sf_full[s]);
+          mbar_expect_tx(sbar, (uint32_t)(kblocks * 512 * (1 + sf_tiles)));
           bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB), p.sfa + ((size_t)ti.sfa_tile * KT + (size_t)ks * KB) * 512,
-                       (uint32_t)kblocks * 512, bar);
+                       (uint32_t)kblocks * 512, sbar);
           for (int j = 0; j < sf_tiles; ++j)
             bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB + C::kStageSFA + j * (KB * 512)),
-                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * KB) * 512, (uint32_t)kblocks * 512, bar);
+                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * KB) * 512, (uint32_t)kblocks * 512, sbar);
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          mbar_expect_tx(bar, (uint32_t)(C::kStageA + C::kStageB));
+          tma_load_2d(smem_u32(st), &map_a, ks * C::kRowBytes, ti.a_row0, bar);
+          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
         }
       }
     }
@@ -320,7 +228,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
       for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
         const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
-        ok = mbar_wait(smem_u32(&full_bar[s]), ph, p.status, 6);
+        ok = mbar_wait(smem_u32(&sf_full[s]), ph, p.status, 6);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const unsigned char* sf = smem + (size_t)s * C::kStageBytes + C::kStageA + C::kStageB;
@@ -335,7 +243,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         tcgen05_wait_st();
         tcgen05_fence_before();
-        mbar_arrive(smem_u32(&sf_ready[s]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sf_ready[s]));
       }
     }
   } else {
@@ -378,7 +287,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // ... hand the accumulator back to the MMA warp, and only then write to global memory, so
       // that the stores overlap the next tile's main loop
       tcgen05_fence_before();
-      mbar_arrive(smem_u32(&acc_empty[acc]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
       if (row < ti.row_end) {
         uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N;
 #pragma unroll
@@ -644,7 +554,7 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
       ((K / 2) % 16) != 0)
     return B200FP4_STATUS_INVALID_VALUE;
   if (!workspace || workspace_bytes < 256 || !aligned(workspace, 16)) return B200FP4_STATUS_ALLOC_FAILED;
-  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return B200FP4_STATUS_INVALID_VALUE;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 512) return B200FP4_STATUS_INVALID_VALUE;
   if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24)) return B200FP4_STATUS_NOT_SUPPORTED;
   if (b200fp4_has_hardware_acceleration() != 1) return B200FP4_STATUS_ARCH_MISMATCH;
   cudaStream_t st = (cudaStream_t)stream;
@@ -662,14 +572,24 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   int bn = tile_n;
   if (bn == 0) bn = (p.m_tiles * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
   const int kb = stage_kblocks();
-  CUtensorMap ma, mb;
-  if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM, kb * 32) ||
-      !make_map(&mb, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn, kb * 32))
-    return B200FP4_STATUS_INTERNAL_ERROR;
   if (cudaMemsetAsync(workspace, 0, 16, st) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
   }
+  if (bn == 512) {
+    // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)
+    CUtensorMap pa, pb;
+    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 128, 128) ||
+        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 128, 128))
+      return B200FP4_STATUS_INTERNAL_ERROR;
+    int rc2 = launch_gemm_pair(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
+    if (rc2 != B200FP4_STATUS_SUCCESS) return rc2;
+    return finish_launch(2);
+  }
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM, kb * 32) ||
+      !make_map(&mb, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn, kb * 32))
+    return B200FP4_STATUS_INTERNAL_ERROR;
   p.g_hdr = nullptr;
   p.g_mtiles = nullptr;
   p.g_alphas = nullptr;
