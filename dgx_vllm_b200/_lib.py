@@ -11,6 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libb200nvfp4.so")
 
 F16, BF16, F32 = 0, 1, 2
+MOE_ROUTER_WEIGHT_ON_INPUT, SPARSE_META_ORDERED = 1, 2     # flags of the sparse entry points
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -35,7 +36,7 @@ SIGNATURES = {
     "b200fp4_grouped_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_moe_unpermute_reduce": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_sparse_workspace_bytes": (_sz, [_i64, _i64, _i64]),
-    "b200fp4_sparse_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200fp4_sparse_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_sparse_gemv_static": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp]),
     "b200fp4_dense_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_sparse_packed_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
@@ -44,7 +45,7 @@ SIGNATURES = {
     "b200fp4_ep_record_bytes": (_sz, [_i64, _i64]),
     "b200fp4_ep_pack": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_fused_sparse_moe_records": (_i32, [_vp, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
-                                                _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
+                                                _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_ep_combine": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_fused_moe_profile_events": (None, [_vp, _vp, _vp]),
     "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,

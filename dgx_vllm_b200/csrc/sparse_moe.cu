@@ -61,6 +61,7 @@ struct GemvArgs {
   const __half* A;  // [rows, K] fp16; the row of pair p is p / a_div
   int64_t lda;
   int a_div;
+  uint32_t a_magic; // 0 if a_div == 1, else floor(2^32 / a_div) + 1: pair / a_div == umulhi(pair, a_magic) for pair < 2^16
   void* out;        // [P, N] (or [P, N/2] in SiLU mode), leading dimension ldo
   int64_t ldo;
   int out_dtype;
@@ -537,6 +538,315 @@ __global__ void zero_unmapped_rows_kernel(const int* __restrict__ mapped, int P,
   for (int n = threadIdx.x; n < N; n += blockDim.x) store_out(out, out_dtype, (int64_t)p * ldo + n, 0.f);
 }
 
+// ------------------------------------------------------------------------------------------ tensor-core GEMV
+//
+// Same work items as sparse_gemv_kernel, but the 2:4 gather and the multiply-accumulate run on the
+// tensor cores: the weights are the sparse A operand of mma.sp m16n8k32 (f16, fp32 accumulate), the
+// reference's metadata bytes are -- after one byte permute -- the instruction's metadata operand, and
+// the (up to four) tokens of the pass are columns of B.  What is left for the CUDA cores is the
+// E2M1 -> half2 decode (cvt.rn.f16x2.e2m1x2 straight from a byte of the loaded word), the E4M3 ->
+// half2 decode of the block scales (cvt.rn.f16x2.e4m3x2) and one half2 multiply per pair of weights
+// (E2M1 x E4M3 is exact in fp16).
+//
+// Requires every 4-group's two indices in increasing order (the instruction's rule), which is how
+// the reference's converter writes them (sparse_v7_moe_patch.py:59-60); callers promise it.
+//
+// A block is 16 warps.  An item is (pass, slab of 128*CG columns); warp w owns column group w % CG
+// and K-slice w / CG and walks its K-slice in steps of 32 k.  One step of one warp reads 8 compressed
+// rows, 4 metadata rows and 2 scale rows of 128 columns (1792 bytes) from a private cp.async ring
+// that keeps running across items, and issues 8 mma.sp (16 columns x 32 k each):
+//   * quad q = lane / 4 owns columns 16q..16q+15 of the warp's 128; mma j takes columns 2h, 2h+1 of
+//     every quad (h = 4*(j%2) + j/2) as its rows q and q+8;
+//   * lane t = lane % 4 of the quad reads compressed rows t and t+4 (the instruction's 4-groups t and
+//     t+4), so byte 2h (2h+1) of those two 16-byte vectors decodes to the fragment registers of row q
+//     (q+8) -- no shuffles;
+//   * metadata: for mma j the lanes with t/2 == j%2 supply it; their register is [row q | row q+8] x
+//     [metadata rows 2(t%2), 2(t%2)+1], i.e. bytes (2h, 2h+1) of two 8-byte loads interleaved by PRMT.
+constexpr int kMmaThreads = 512;
+constexpr int kMmaWarps = 16;
+constexpr int kMmaStageBytes = 1792;
+constexpr int kMmaRedBytes = kMmaWarps * 128 * 4 * 4;   // K-slice partial sums [warp][column][token] fp32
+
+__device__ __forceinline__ uint32_t shared_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t lds32_at(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 lds64_at(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 lds128_at(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 lds128f_at(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts64f_at(uint32_t a, float x, float y) {
+  asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(x), "f"(y) : "memory");
+}
+__device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+template <int SEL>
+__device__ __forceinline__ void mma_sp_m16n8k32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                const uint32_t (&b)[4], uint32_t e) {
+  asm volatile(
+      "mma.sp::ordered_metadata.sync.aligned.m16n8k32.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9,%10,%11}, {%0,%1,%2,%3}, %12, %13;"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(e), "n"(SEL));
+}
+
+// byte B of a word holds two E2M1 values -> half2 (low nibble in the low half)
+template <int B>
+__device__ __forceinline__ __half2 e2m1x2_to_h2(uint32_t w) {
+  uint32_t r;
+  if (B == 0) asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b0; }" : "=r"(r) : "r"(w));
+  else if (B == 1) asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b1; }" : "=r"(r) : "r"(w));
+  else if (B == 2) asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b2; }" : "=r"(r) : "r"(w));
+  else asm("{ .reg .b8 b0, b1, b2, b3; mov.b32 {b0, b1, b2, b3}, %1; cvt.rn.f16x2.e2m1x2 %0, b3; }" : "=r"(r) : "r"(w));
+  return as_h2(r);
+}
+// half H (16 bits) of a word holds two E4M3 values -> half2
+template <int H>
+__device__ __forceinline__ __half2 e4m3x2_to_h2(uint32_t w) {
+  uint32_t r;
+  if (H == 0) asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(r) : "r"(w));
+  else asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(r) : "r"(w));
+  return as_h2(r);
+}
+
+template <int CG, int S, bool kSilu>
+__global__ void __launch_bounds__(kMmaThreads, 1)
+    sparse_gemv_mma_kernel(const GemvArgs g) {
+  constexpr int KSL = kMmaWarps / CG;          // K-slices per item
+  constexpr int VCOLS = 128 * CG;              // columns of a slab (SiLU: 64*CG gate + 64*CG up)
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q = lane >> 2, t = lane & 3;
+  const int cgw = warp % CG, ks = warp / CG;
+  const int K = g.K;
+  const int nstep = K / (32 * KSL);
+  const int grid = gridDim.x;
+
+  // ---- shared memory map (shared-window addresses)
+  //   activations of the current and the next pass [2][4][K + 8] fp16 | partial sums | 16 rings of S stages
+  const uint32_t a_pitch = 2u * (uint32_t)K + 16u;
+  const uint32_t sa = (shared_addr(smem) + 1023u) & ~1023u;
+  const uint32_t red = sa + ((8u * a_pitch + 1023u) & ~1023u);
+  const uint32_t ring_bytes = S * kMmaStageBytes;
+  const uint32_t ring = red + kMmaRedBytes + (uint32_t)warp * ring_bytes;
+  const uint32_t ring_end = ring + ring_bytes;
+
+  // ---- items of this block: blockIdx.x, + grid, ...
+  const int n_slabs = g.n_slabs;
+  const int n_items = g.plan.hdr[1] * n_slabs;
+  const int my_items = (int)blockIdx.x < n_items ? (n_items - 1 - (int)blockIdx.x) / grid + 1 : 0;
+  if (my_items == 0) return;
+  auto pass_of = [&](int i) { return ((int)blockIdx.x + i * grid) / n_slabs; };
+  Rec rc = load_rec(g.plan.pass_rec, pass_of(0));
+  Rec rn = my_items > 1 ? load_rec(g.plan.pass_rec, pass_of(1)) : empty_rec();
+  int e_nn = my_items > 2 ? g.plan.pass_rec[2 * pass_of(2)].x : -1;
+
+  const int chunks = K >> 3;
+  auto issue_A = [&](const Rec& r, int buf) {
+#pragma unroll
+    for (int tk = 0; tk < 4; ++tk)
+      if (tk < r.nt) {
+        const uint32_t pr = (uint32_t)r.pair(tk);
+        const int64_t row = g.a_magic ? (int64_t)__umulhi(pr, g.a_magic) : (int64_t)pr;
+        const __half* src = g.A + row * g.lda;
+        const uint32_t dst = sa + (uint32_t)(buf * 4 + tk) * a_pitch;
+        for (int ch = tid; ch < chunks; ch += kMmaThreads) cp_async16_s(dst + (uint32_t)ch * 16u, src + ch * 8);
+      }
+  };
+
+  // ---- weight fetch stream of this warp: lane = (row fr, 16-byte chunk fc) of every tensor's tile.
+  // It runs S-1 stages ahead of the compute and crosses item boundaries (at most two items ahead).
+  const int fr = lane >> 3, fc = lane & 7;
+  const int64_t comp_step = 4 * g.w.comp_pair * KSL, meta_step = 4 * g.w.meta_row * KSL, scale_step = 2 * g.w.scale_row * KSL;
+  const int64_t comp_row4 = 2 * g.w.comp_pair;
+  const int64_t lane_comp = (int64_t)(4 * ks + (fr >> 1)) * g.w.comp_pair + (fr & 1) * g.w.comp_odd;
+  const int64_t lane_meta = (int64_t)(4 * ks + fr) * g.w.meta_row;
+  const int64_t lane_scale = (int64_t)(2 * ks + fr) * g.w.scale_row;
+  const int lane_v = cgw * 128 + fc * 16;   // virtual column of this lane's chunk in the slab
+  int i_cur = 0;                            // ordinal of the item being computed
+  int f_i = 0, f_j = 0;
+  uint32_t f_dst = ring + (uint32_t)lane * 16u;
+  const uint8_t *f_comp = nullptr, *f_meta = nullptr, *f_scale = nullptr;
+  auto fetch_next = [&]() {
+    if (f_i < my_items) {
+      if (f_j == 0) {
+        const int rel = f_i - i_cur;
+        const int e = rel == 0 ? rc.e : (rel == 1 ? rn.e : e_nn);
+        const int slab = ((int)blockIdx.x + f_i * grid) % n_slabs;
+        int col;
+        if (kSilu) col = lane_v < 64 * CG ? slab * (64 * CG) + lane_v : g.inter + slab * (64 * CG) + (lane_v - 64 * CG);
+        else col = slab * VCOLS + lane_v;
+        f_comp = g.w.comp + ((int64_t)e * g.w.comp_e + col + lane_comp);
+        f_meta = g.w.meta + ((int64_t)e * g.w.meta_e + col + lane_meta);
+        f_scale = g.w.scale + ((int64_t)e * g.w.scale_e + col + lane_scale);
+      }
+      cp_async16_s(f_dst, f_comp);
+      cp_async16_s(f_dst + 512u, f_comp + comp_row4);
+      cp_async16_s(f_dst + 1024u, f_meta);
+      if (lane < 16) cp_async16_s(f_dst + 1536u, f_scale);
+      f_comp += comp_step;
+      f_meta += meta_step;
+      f_scale += scale_step;
+      if (++f_j == nstep) {
+        f_j = 0;
+        ++f_i;
+      }
+    }
+    cp_async_commit();
+    f_dst += kMmaStageBytes;
+    if (f_dst >= ring_end) f_dst -= ring_bytes;
+  };
+
+  issue_A(rc, 0);
+  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < S - 1; ++s) fetch_next();
+
+  // lane-constant pieces of the addresses used in a step
+  const uint32_t off_comp = (uint32_t)t * 128u + (uint32_t)q * 16u;
+  const uint32_t off_meta = 1024u + (uint32_t)(2 * (t & 1)) * 128u + (uint32_t)q * 16u + (uint32_t)(t >> 1) * 8u;
+  const uint32_t off_scale = 1536u + (uint32_t)q * 16u;
+  const uint32_t off_b = (uint32_t)q * a_pitch + (uint32_t)t * 4u + (uint32_t)ks * 64u;   // token q, k = 32*ks + 2t (+8i)
+  // scratch [warp][column 0..127][token 0..3]; the 16-byte token groups of a column are XOR-swizzled
+  // by the column's quad so that neither side has bank conflicts
+  const uint32_t red_w = red + (uint32_t)warp * 2048u + (uint32_t)q * 256u + 8u * (uint32_t)(t & 1) +
+                         16u * (uint32_t)((q ^ ((cgw & 1) << 2)) & 7);
+
+  uint32_t c_st = ring;
+  int abuf = 0;
+  for (; i_cur < my_items; ++i_cur) {
+    const int slab = ((int)blockIdx.x + i_cur * grid) % n_slabs;
+    Rec rnn = i_cur + 2 < my_items ? load_rec(g.plan.pass_rec, pass_of(i_cur + 2)) : empty_rec();
+    const int e_n3 = i_cur + 3 < my_items ? g.plan.pass_rec[2 * pass_of(i_cur + 3)].x : -1;
+    const float gmul = g.w.g[rc.e];
+    // the group that carried this pass's activations is followed by nstep - 1 newer ones
+    if (nstep >= S - 1) cp_async_wait<S - 2>();
+    else if (nstep == 2) cp_async_wait<1>();
+    else cp_async_wait<(S > 3 ? 2 : 1)>();
+    __syncthreads();   // activations of this pass complete for all threads; scratch and the other buffer free
+    issue_A(rn, abuf ^ 1);   // rides on the next committed weight stage
+
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
+    uint32_t ab = sa + (uint32_t)abuf * 4u * a_pitch + off_b;
+
+    for (int js = 0; js < nstep; ++js) {
+      cp_async_wait<S - 2>();
+      __syncwarp();
+      const uint32_t st = c_st;
+      const uint4 v0 = lds128_at(st + off_comp), v1 = lds128_at(st + off_comp + 512u);
+      const uint2 m0 = lds64_at(st + off_meta), m1 = lds64_at(st + off_meta + 128u);
+      const uint4 s0 = lds128_at(st + off_scale), s1 = lds128_at(st + off_scale + 128u);
+      uint32_t b[4] = {0u, 0u, 0u, 0u};
+      if (q < 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b[k] = lds32_at(ab + 16u * k);
+      }
+      ab += 64u * KSL;
+      c_st += kMmaStageBytes;
+      if (c_st >= ring_end) c_st -= ring_bytes;
+      fetch_next();   // into the slot read in the previous step (all lanes are past this step's __syncwarp)
+      uint32_t em[4];
+      em[0] = prmt(m0.x, m1.x, 0x5140u);
+      em[1] = prmt(m0.x, m1.x, 0x7362u);
+      em[2] = prmt(m0.y, m1.y, 0x5140u);
+      em[3] = prmt(m0.y, m1.y, 0x7362u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // mma j: columns 2h, 2h+1 of the quad = bytes (2hf, 2hf+1) of word wi of every loaded vector
+        constexpr int kH[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+        const int h = kH[j];
+        const int wi = h >> 1, hf = h & 1;
+        const uint32_t c0 = word_of(v0, wi), c1 = word_of(v1, wi);
+        const __half2 sc0 = hf ? e4m3x2_to_h2<1>(word_of(s0, wi)) : e4m3x2_to_h2<0>(word_of(s0, wi));
+        const __half2 sc1 = hf ? e4m3x2_to_h2<1>(word_of(s1, wi)) : e4m3x2_to_h2<0>(word_of(s1, wi));
+        const __half2 a0 = __hmul2(hf ? e2m1x2_to_h2<2>(c0) : e2m1x2_to_h2<0>(c0), __low2half2(sc0));
+        const __half2 a1 = __hmul2(hf ? e2m1x2_to_h2<3>(c0) : e2m1x2_to_h2<1>(c0), __high2half2(sc0));
+        const __half2 a2 = __hmul2(hf ? e2m1x2_to_h2<2>(c1) : e2m1x2_to_h2<0>(c1), __low2half2(sc1));
+        const __half2 a3 = __hmul2(hf ? e2m1x2_to_h2<3>(c1) : e2m1x2_to_h2<1>(c1), __high2half2(sc1));
+        if ((j & 1) == 0)
+          mma_sp_m16n8k32<0>(acc[j], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                             *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), b, em[j >> 1]);
+        else
+          mma_sp_m16n8k32<1>(acc[j], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                             *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), b, em[j >> 1]);
+      }
+    }
+
+    // partial sums of this K-slice -> scratch
+    if (2 * t < rc.nt) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        constexpr int kH[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+        const uint32_t c0 = 2u * kH[j], c1 = 2u * kH[j] + 1u;   // columns of the quad: rows q and q+8 of mma j
+        sts64f_at((red_w ^ ((c0 & 7u) << 4)) + (c0 >> 3) * 128u, acc[j][0], acc[j][1]);
+        sts64f_at((red_w ^ ((c1 & 7u) << 4)) + (c1 >> 3) * 128u, acc[j][2], acc[j][3]);
+      }
+    }
+    __syncthreads();
+    // epilogue, spread over all warps: one (column, token) sum per lane and round.  The warp of
+    // K-slice s and column group cw is s * CG + cw.
+    auto slice_sum = [&](int v, int tok) {
+      const int cw = v >> 7, col = v & 127;
+      const uint32_t a = red + (uint32_t)cw * 2048u + (((uint32_t)col * 16u) ^ ((uint32_t)(((col >> 4) ^ ((cw & 1) << 2)) & 7) << 4)) +
+                         (uint32_t)tok * 4u;
+      float sum = 0.f;
+#pragma unroll
+      for (int s = 0; s < KSL; ++s) sum += __uint_as_float(lds32_at(a + (uint32_t)(s * CG) * 2048u));
+      return sum;
+    };
+    if (kSilu) {
+#pragma unroll
+      for (int r = 0; r < CG; ++r) {
+        const int idx = r * 256 + warp * 16 + (lane & 15);
+        const int col_g = idx >> 2, tok = idx & 3;
+        const float sum = slice_sum(col_g + (lane >> 4) * (64 * CG), tok);
+        const float other = __shfl_down_sync(0xffffffffu, sum, 16);
+        if (lane < 16 && tok < rc.nt) {
+          const float gate = sum * gmul, up = other * gmul;
+          store_out(g.out, g.out_dtype, (int64_t)rc.pair(tok) * g.ldo + slab * (64 * CG) + col_g,
+                    gate / (1.0f + __expf(-gate)) * up);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < CG; ++r) {
+        const int x = r * 512 + tid;
+        const int v = x >> 2, tok = x & 3;
+        const float sum = slice_sum(v, tok);
+        if (tok < rc.nt) store_out(g.out, g.out_dtype, (int64_t)rc.pair(tok) * g.ldo + slab * VCOLS + v, sum * gmul);
+      }
+    }
+    rc = rn;
+    rn = rnn;
+    e_nn = e_n3;
+    abuf ^= 1;
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------------ generic
 
 // Scalar kernel for shapes the vectorised kernel does not take (N % 16 != 0, unusual scale group
@@ -683,6 +993,67 @@ int launch_gemv_t(const GemvArgs& g, int64_t grid, size_t smem, cudaStream_t st)
   return B200FP4_STATUS_SUCCESS;
 }
 
+// ---- tensor-core kernel: configuration and launch
+struct MmaCfg {
+  int cg, stages;
+  bool ok;
+};
+
+size_t mma_smem_bytes(int64_t K, int stages) {
+  const size_t a_bytes = align_up((size_t)8 * (2 * (size_t)K + 16), 1024);
+  return 1024 + a_bytes + kMmaRedBytes + (size_t)kMmaWarps * stages * kMmaStageBytes;
+}
+
+MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu) {
+  MmaCfg c = {0, 0, false};
+  if (G != K / 16 || K % 32 != 0) return c;
+  const int order_silu[3] = {2, 4, 1}, order_plain[3] = {4, 2, 1};
+  for (int i = 0; i < 3; ++i) {
+    const int cg = inter_silu > 0 ? order_silu[i] : order_plain[i];
+    const int ksl = kMmaWarps / cg;
+    const bool cols_ok = inter_silu > 0 ? (inter_silu % (64 * cg) == 0 && N == 2 * (int64_t)inter_silu) : (N % (128 * cg) == 0);
+    if (cols_ok && K % (32 * ksl) == 0 && K / (32 * ksl) >= 2) {
+      for (int s = 5; s >= 3; s -= 2)
+        if (mma_smem_bytes(K, s) <= 227 * 1024 && (s - 2 < 2 * (int)(K / (32 * ksl)))) {
+          c.cg = cg;
+          c.stages = s;
+          c.ok = true;
+          return c;
+        }
+    }
+  }
+  return c;
+}
+
+template <int CG, int S, bool kSilu>
+int launch_mma_t(const GemvArgs& g, int64_t grid, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(sparse_gemv_mma_kernel<CG, S, kSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             227 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return B200FP4_STATUS_EXECUTION_FAILED;
+    }
+    attr_set[dev] = true;
+  }
+  sparse_gemv_mma_kernel<CG, S, kSilu><<<(unsigned)grid, kMmaThreads, mma_smem_bytes(g.K, S), st>>>(g);
+  return B200FP4_STATUS_SUCCESS;
+}
+
+template <bool kSilu>
+int launch_mma(const GemvArgs& g, const MmaCfg& c, int64_t grid, cudaStream_t st) {
+  if (c.stages == 5) {
+    if (c.cg == 1) return launch_mma_t<1, 5, kSilu>(g, grid, st);
+    if (c.cg == 2) return launch_mma_t<2, 5, kSilu>(g, grid, st);
+    return launch_mma_t<4, 5, kSilu>(g, grid, st);
+  }
+  if (c.cg == 1) return launch_mma_t<1, 3, kSilu>(g, grid, st);
+  if (c.cg == 2) return launch_mma_t<2, 3, kSilu>(g, grid, st);
+  return launch_mma_t<4, 3, kSilu>(g, grid, st);
+}
+
 template <bool kScale8, bool kSilu>
 int launch_gemv(const GemvArgs& g, const GemvCfg& c, int64_t grid, cudaStream_t st) {
   if (c.cg == 32) return launch_gemv_t<256, 16, 32, 2, kScale8, kSilu>(g, grid, c.smem, st);
@@ -738,13 +1109,14 @@ void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
 int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
                    int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int inter_silu,
-                   cudaStream_t st) {
+                   bool meta_ordered, cudaStream_t st) {
   GemvArgs g;
   g.w = w;
   g.plan = plan;
   g.A = A;
   g.lda = lda;
   g.a_div = a_div;
+  g.a_magic = a_div > 1 ? (uint32_t)(((uint64_t)1 << 32) / (uint64_t)a_div) + 1u : 0u;
   g.out = out;
   g.ldo = ldo;
   g.out_dtype = out_dtype;
@@ -752,6 +1124,17 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
   g.K = (int)K;
   g.inter = inter_silu;
   const bool s8 = (G == K / 8);
+  if (meta_ordered) {
+    // tensor-core kernel where the shape allows it (one scale per 16 k, whole 128-column groups)
+    const MmaCfg mc = pick_mma_cfg(N, K, G, inter_silu);
+    if (mc.ok) {
+      g.n_slabs = inter_silu > 0 ? inter_silu / (64 * mc.cg) : (int)(N / (128 * mc.cg));
+      int64_t grid = max_passes(P, E) * g.n_slabs;
+      if (grid > (int64_t)sm_count()) grid = sm_count();
+      if (grid < 1) grid = 1;
+      return inter_silu > 0 ? launch_mma<true>(g, mc, grid, st) : launch_mma<false>(g, mc, grid, st);
+    }
+  }
   const GemvCfg c = pick_cfg(K, s8);
   if (!c.ok) return B200FP4_STATUS_NOT_SUPPORTED;
   const int slab = c.cg * c.cols;
@@ -764,8 +1147,8 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
 }
 
 int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, const int32_t* expert_ids, void* out,
-               int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, void* workspace, size_t ws_bytes,
-               void* stream) {
+               int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int flags, void* workspace,
+               size_t ws_bytes, void* stream) {
   int rc = check_common(A, a_dtype, out, out_dtype, P, N, K, G, E);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (P == 0) return B200FP4_STATUS_SUCCESS;
@@ -780,7 +1163,7 @@ int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, con
     launch_plan(expert_ids, P, 1, 1, nullptr, 0, E, plan, a_bf16 ? A : nullptr, a16, P, K, K, st);
     zero_unmapped_rows_kernel<<<(unsigned)P, 128, 0, st>>>(plan.mapped, (int)P, out, out_dtype, N, (int)N);
     rc = run_projection(w, plan, a_bf16 ? a16 : reinterpret_cast<const __half*>(A), K, 1, out, out_dtype, N, P, N, K,
-                        G, E, 0, st);
+                        G, E, 0, (flags & B200FP4_SPARSE_META_ORDERED) != 0, st);
     if (rc != B200FP4_STATUS_SUCCESS) return rc;
     return finish_launch(3);
   }
@@ -802,8 +1185,8 @@ extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E
 
 extern "C" int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B_comp_T, const uint8_t* Meta_T_pk,
                                    const uint8_t* scales_T, const float* g_scales, const int32_t* expert_ids, void* out,
-                                   int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, void* workspace,
-                                   size_t workspace_bytes, void* stream) {
+                                   int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int flags,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
   SparseWeights w;
   w.comp = B_comp_T;
   w.meta = Meta_T_pk;
@@ -816,7 +1199,7 @@ extern "C" int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B_
   w.meta_row = N;
   w.scale_e = G * N;
   w.scale_row = N;
-  return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, G, E, workspace, workspace_bytes, stream);
+  return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, G, E, flags, workspace, workspace_bytes, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -877,7 +1260,7 @@ extern "C" int b200fp4_sparse_gemv_static(const void* A, int a_dtype, const uint
   const int rc = static_scratch_ptr(&scratch);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return b200fp4_sparse_gemv(A, a_dtype, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, out, out_dtype, P, N, K, G,
-                             E, scratch, kStaticScratchBytes, stream);
+                             E, 0, scratch, kStaticScratchBytes, stream);
 }
 
 extern "C" int b200fp4_dense_gemv(const void* A, int a_dtype, const uint8_t* B_dense_T, const uint8_t* scales_T,
@@ -920,7 +1303,7 @@ extern "C" int b200fp4_sparse_packed_gemv(const void* A, int a_dtype, const uint
   w.meta_row = 4 * N;
   w.scale_e = w.comp_e;
   w.scale_row = 4 * N;
-  return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, K / 8, E, workspace, workspace_bytes, stream);
+  return gemv_entry(w, 0, A, a_dtype, expert_ids, out, out_dtype, P, N, K, K / 8, E, 0, workspace, workspace_bytes, stream);
 }
 
 extern "C" void b200fp4_fused_moe_profile_events(void* before_gate_up, void* after_gate_up, void* after_down) {
@@ -942,8 +1325,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
                           const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
                           int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
                           const float* w2_g, int64_t G2, void* out, int out_dtype, int64_t M, int64_t topk, int64_t H,
-                          int64_t I, int64_t E, int apply_router_weight_on_input, void* workspace, size_t workspace_bytes,
-                          void* stream) {
+                          int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return B200FP4_STATUS_INVALID_VALUE;
   if (ld_h < H || ld_w < topk || ld_ids < topk || (ld_h % 8) != 0) return B200FP4_STATUS_INVALID_VALUE;
   const int64_t P = M * topk;
@@ -979,19 +1361,20 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   off += align_up((size_t)P * I * sizeof(__half), 256);
   float* down = reinterpret_cast<float*>(ws + off);
   const bool bf = h_dtype == B200FP4_DTYPE_BF16;
+  const bool ordered = (flags & B200FP4_SPARSE_META_ORDERED) != 0;
 
   launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M, H, ld_h, st);
   if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
   rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk, act,
-                      B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, st);
+                      B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, ordered, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
-  rc = run_projection(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, st);
+  rc = run_projection(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, ordered, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);
   weighted_reduce_kernel<<<grid, 256, 0, st>>>(down, topk_weights, plan.mapped, out, out_dtype, (int)M, (int)topk,
-                                               (int)H, apply_router_weight_on_input ? 1 : 0, ld_w);
+                                               (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
   return finish_launch(4);
 }
 
@@ -1000,12 +1383,11 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
                                         const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
                                         const float* w13_g, int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta,
                                         const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out, int out_dtype,
-                                        int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
-                                        int apply_router_weight_on_input, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
+                                        int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E, int flags,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
   return fused_moe_impl(hidden, H, h_dtype, topk_weights, topk, topk_ids, topk, expert_map, global_E, w13_comp, w13_meta,
-                        w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out, out_dtype, M, topk, H, I, E,
-                        apply_router_weight_on_input, workspace, workspace_bytes, stream);
+                        w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out, out_dtype, M, topk, H, I, E, flags,
+                        workspace, workspace_bytes, stream);
 }
 
 // ------------------------------------------------------------------------------------------ expert parallel
@@ -1094,11 +1476,12 @@ extern "C" int b200fp4_fused_sparse_moe_records(const void* records, int64_t rec
                                                 int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta,
                                                 const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out,
                                                 int out_dtype, int64_t T, int64_t topk, int64_t H, int64_t I, int64_t E,
-                                                void* workspace, size_t workspace_bytes, void* stream) {
+                                                int flags, void* workspace, size_t workspace_bytes, void* stream) {
   if (!records || record_bytes != (int64_t)b200fp4_ep_record_bytes(H, topk)) return B200FP4_STATUS_INVALID_VALUE;
   const unsigned char* r = reinterpret_cast<const unsigned char*>(records);
   return fused_moe_impl(r, record_bytes / 2, h_dtype, reinterpret_cast<const float*>(r + H * 2 + topk * 4),
                         record_bytes / 4, reinterpret_cast<const int32_t*>(r + H * 2), record_bytes / 4, expert_map,
                         global_E, w13_comp, w13_meta, w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out,
-                        out_dtype, T, topk, H, I, E, 0, workspace, workspace_bytes, stream);
+                        out_dtype, T, topk, H, I, E, flags & ~B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT, workspace, workspace_bytes,
+                        stream);
 }

@@ -68,6 +68,7 @@ class ExpertParallelMoE:
         self._emap = None
         self._fn = local_moe_fn
         self._bufs = {}
+        self._flags = None
 
     def _cuda_local(self, hidden, topk_w, topk_ids, emap):
         from . import sparse_fp4_v7 as sp7
@@ -121,6 +122,10 @@ class ExpertParallelMoE:
         ws = workspace(dev, L.b200fp4_fused_moe_workspace_bytes(T, topk, H, self.inter, E))
         out = torch.empty(B, H, dtype=hidden.dtype, device=dev)
         code = dtype_code(hidden.dtype)
+        if self._flags is None:   # ordered metadata -> tensor-core GEMVs; checked once per layer
+            from .sparse_fp4_v7 import metadata_ordered
+            ok = metadata_ordered(self.w13["meta_T"]) and metadata_ordered(self.w2["meta_T"])
+            self._flags = _lib.SPARSE_META_ORDERED if ok else 0
         with torch.cuda.device(dev):
             _lib.check(L.b200fp4_ep_pack(ptr(hidden), ptr(ids), ptr(tw), B, H, topk, G, ptr(send), stream_ptr(dev)), "ep_pack")
             dist.all_to_all_single(recv, send, group=self.group)                                   # dispatch
@@ -128,7 +133,8 @@ class ExpertParallelMoE:
                 ptr(recv), R, code, ptr(emap), emap.numel(),
                 *[ptr(self.w13[x]) for x in k], self.w13["scale_T"].shape[1],
                 *[ptr(self.w2[x]) for x in k], self.w2["scale_T"].shape[1],
-                ptr(part), code, T, topk, H, self.inter, E, ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_records")
+                ptr(part), code, T, topk, H, self.inter, E, self._flags, ptr(ws), ws.numel(), stream_ptr(dev)),
+                "fused_sparse_moe_records")
             dist.all_to_all_single(back, part, group=self.group)                                   # combine
             _lib.check(L.b200fp4_ep_combine(ptr(back), code, B, H, G, ptr(out), stream_ptr(dev)), "ep_combine")
         return out

@@ -9,7 +9,12 @@ sm_100a kernels in libb200nvfp4.so.  Differences a caller can observe:
     (the reference casts bf16 to fp16 first and always returns fp16); pass out_dtype to force one;
   * expert ids outside [0, E) -- e.g. -1 from an expert-parallel expert_map -- give a zero
     contribution instead of an out-of-bounds read;
-  * the sign bit of a block scale is ignored (block scales are magnitudes).
+  * when every 4-group's two metadata indices are in increasing order -- which is how the
+    reference's converter writes them (sparse_v7_moe_patch.py:59-60) -- the GEMVs run on the tensor
+    cores.  The mirrors check each metadata tensor object once (`metadata_ordered`) unless the
+    caller passes `meta_ordered=`; tensors with other index pairs take the general kernel, which
+    accepts anything the reference kernel accepts.  (A block scale's sign bit, never set by an
+    NVFP4 quantizer, is honoured by the tensor-core kernel and ignored by the general one.)
 """
 from __future__ import annotations
 
@@ -42,12 +47,47 @@ def _out_dtype(A: torch.Tensor, out_dtype) -> torch.dtype:
     return A.dtype if out_dtype is None else out_dtype
 
 
-def batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, *, out_dtype=None):
+def metadata_ordered(meta: torch.Tensor) -> bool:
+    """True if in every byte of `meta` (two 4-groups: i0 | i1<<2 | i0'<<4 | i1'<<6) i0 < i1 and i0' < i1'.
+
+    The answer is remembered on the tensor object (with its version counter, so an in-place update
+    is checked again).  The first call per tensor reads the whole tensor and synchronises; while a
+    CUDA graph is being captured an unseen tensor is reported as not ordered instead (the general
+    kernel is always valid)."""
+    seen = getattr(meta, "_b200fp4_meta_ordered", None)
+    if seen is not None and seen[0] == meta._version:
+        return seen[1]
+    if meta.is_cuda and torch.cuda.is_current_stream_capturing():
+        return False
+    flat = meta.reshape(-1).view(torch.uint8)
+    ok = True
+    step = 1 << 26
+    for off in range(0, flat.numel(), step):
+        m = flat[off:off + step]
+        lo, hi = m & 0x33, (m >> 2) & 0x33          # (i0, i0') and (i1, i1') in bits 0-1 and 4-5
+        if not bool(((hi & 3) > (lo & 3)).all() and ((hi >> 4) > (lo >> 4)).all()):
+            ok = False
+            break
+    try:
+        meta._b200fp4_meta_ordered = (meta._version, ok)
+    except AttributeError:
+        pass
+    return ok
+
+
+def _flags(meta_ordered, *metas) -> int:
+    if meta_ordered is None:
+        meta_ordered = all(metadata_ordered(m) for m in metas)
+    return _lib.SPARSE_META_ORDERED if meta_ordered else 0
+
+
+def batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, *, out_dtype=None, meta_ordered=None):
     """out[p] = A[p] . W[expert_ids[p]]^T with W given in 2:4 compressed NVFP4 form
     (batched_sparse_v7, sparse_fp4_v7.cu:374-406).
 
     A [P,K] f16/bf16; B_comp_T [E,K/4,N] u8; Meta_T_pk [E,K/8,N] u8; scales_T [E,G,N] e4m3 bytes
-    (G = K/16 or K/8 vectorised, any divisor of K/8 otherwise); g_scales [E] f32; expert_ids [P]."""
+    (G = K/16 or K/8 vectorised, any divisor of K/8 otherwise); g_scales [E] f32; expert_ids [P].
+    meta_ordered: promise (True) / deny (False) ordered metadata indices, or None to check once."""
     dev = require_cuda(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids)
     _check_act(A, "A")
     _check_u8(B_comp_T, "B_comp_T"), _check_u8(Meta_T_pk, "Meta_T_pk"), _check_u8(scales_T, "scales_T")
@@ -67,7 +107,8 @@ def batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids, *,
     with torch.cuda.device(dev):
         _lib.check(L.b200fp4_sparse_gemv(ptr(A), dtype_code(A.dtype), ptr(B_comp_T), ptr(Meta_T_pk), ptr(scales_T),
                                          ptr(g_scales), ptr(ids), ptr(out), dtype_code(out.dtype), P, N, K, G, E,
-                                         ptr(ws), ws.numel(), stream_ptr(dev)), "batched_sparse_v7")
+                                         _flags(meta_ordered, Meta_T_pk), ptr(ws), ws.numel(), stream_ptr(dev)),
+                   "batched_sparse_v7")
     return out
 
 
@@ -120,13 +161,13 @@ def batched_sparse_packed_v7(A, B_packed_T, g_scales, expert_ids, orig_K, *, out
 def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
                         w13_comp, w13_meta, w13_scale, w13_g_scales,
                         w2_comp, w2_meta, w2_scale, w2_g_scales,
-                        inter_size, apply_router_weight_on_input, *, out_dtype=None):
+                        inter_size, apply_router_weight_on_input, *, out_dtype=None, meta_ordered=None):
     """One MoE layer for decode (fused_sparse_moe_v7, sparse_fp4_v7.cu:607-742):
     gate_up GEMV -> SiLU(gate)*up -> down GEMV -> router-weighted sum.
 
     hidden_states [M,H] f16/bf16; topk_weights [M,topk] f32; topk_ids [M,topk] int; expert_map [global_E]
     int32 or an empty tensor / None for identity; w13_* [E,H/4,2I], [E,H/8,2I], [E,G,2I], [E];
-    w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H]."""
+    w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H].  meta_ordered as in batched_sparse_v7."""
     dev = require_cuda(hidden_states, topk_weights, topk_ids, w13_comp, w13_meta, w13_scale, w13_g_scales,
                        w2_comp, w2_meta, w2_scale, w2_g_scales)
     _check_act(hidden_states, "hidden_states")
@@ -166,7 +207,8 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
             0 if emap is None else emap.numel(),
             ptr(w13_comp), ptr(w13_meta), ptr(w13_scale), ptr(w13_g_scales), w13_scale.shape[1],
             ptr(w2_comp), ptr(w2_meta), ptr(w2_scale), ptr(w2_g_scales), w2_scale.shape[1],
-            ptr(out), dtype_code(out.dtype), M, topk, H, I, E, 1 if apply_router_weight_on_input else 0,
+            ptr(out), dtype_code(out.dtype), M, topk, H, I, E,
+            (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0) | _flags(meta_ordered, w13_meta, w2_meta),
             ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_v7")
     return out
 

@@ -133,7 +133,20 @@ B200FP4_API int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, con
  *   out        [P, N] (out_dtype f16 or bf16)
  *   workspace  b200fp4_sparse_workspace_bytes(P, K, E) bytes of scratch, 256-byte aligned
  * N % 16 == 0 selects the vectorised kernel; other N fall back to a scalar kernel.
+ *
+ * flags (also the `flags` of the fused layer below):
+ *   B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT  fused layer only, see there
+ *   B200FP4_SPARSE_META_ORDERED         the caller promises that in every 4-group of Meta_T_pk the
+ *       first 2-bit index is smaller than the second.  That is how the reference's converter writes
+ *       them (sparse_v7_moe_patch.py:59-60, top-2 positions sorted) and what
+ *       b200fp4_convert_to_sparse_2of4 produces.  With the promise (and G = K/16, N a multiple of
+ *       512, or of 256 / 128 as K allows) the GEMV runs on the tensor cores (mma.sp, whose metadata
+ *       operand requires ordered indices); results with unordered or repeated indices are then
+ *       undefined.  Without it any index pair is accepted, as in the reference kernel.
  * ------------------------------------------------------------------------------------------- */
+#define B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT 1
+#define B200FP4_SPARSE_META_ORDERED 2
+
 B200FP4_API size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E);
 
 /* batched_sparse_v7(A, B_comp_T, Meta_T_pk, scales_T, g_scales, expert_ids),
@@ -142,9 +155,10 @@ B200FP4_API int b200fp4_sparse_gemv(const void* A, int a_dtype, const uint8_t* B
                                     const uint8_t* Meta_T_pk, const uint8_t* scales_T,
                                     const float* g_scales, const int32_t* expert_ids, void* out,
                                     int out_dtype, int64_t P, int64_t N, int64_t K, int64_t G,
-                                    int64_t E, void* workspace, size_t workspace_bytes, void* stream);
+                                    int64_t E, int flags, void* workspace, size_t workspace_bytes,
+                                    void* stream);
 
-/* b200fp4_sparse_gemv without a caller workspace.  No counterpart in the reference: it exists
+/* b200fp4_sparse_gemv (flags = 0) without a caller workspace.  No counterpart in the reference: it exists
  * for hosts that cannot allocate device memory around the call -- e.g. a plug-in inside a serving
  * process whose pool already owns the GPU's memory, or a loop that bans cudaMalloc/cudaFree because
  * they synchronise the device.  The scratch is a fixed ~4.2 MB array inside the library (resident on
@@ -197,8 +211,9 @@ B200FP4_API int b200fp4_convert_to_sparse_2of4(const uint8_t* codes, const uint8
  *   w2_*        comp [E, I/4, H],  meta [E, I/8, H],  scale [E, G2, H],  g [E]
  *   out         [M, H] (out_dtype)
  *   workspace   b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E) bytes
- * apply_router_weight_on_input != 0 sums the expert outputs unweighted, exactly as the reference
- * kernel does (sparse_fp4_v7.cu:592-594). */
+ * flags: B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT (the reference's apply_router_weight_on_input) sums the
+ * expert outputs unweighted, exactly as the reference kernel does (sparse_fp4_v7.cu:592-594);
+ * B200FP4_SPARSE_META_ORDERED as described above, for both weight sets. */
 B200FP4_API size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I,
                                                      int64_t E);
 B200FP4_API int b200fp4_fused_sparse_moe(
@@ -207,7 +222,7 @@ B200FP4_API int b200fp4_fused_sparse_moe(
     const uint8_t* w13_scale, const float* w13_g, int64_t G13, const uint8_t* w2_comp,
     const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g, int64_t G2, void* out,
     int out_dtype, int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
-    int apply_router_weight_on_input, void* workspace, size_t workspace_bytes, void* stream);
+    int flags, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Part 4 -- grouped (per-expert) NVFP4 GEMM for MoE prefill and its routing helpers.
@@ -261,7 +276,7 @@ B200FP4_API int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, 
  *   b200fp4_ep_pack       writes records[g][b] for every destination rank g (send buffer of the
  *                         fixed-capacity all-to-all)
  *   b200fp4_fused_sparse_moe_records   b200fp4_fused_sparse_moe over T received records read in
- *                         place (router weights always applied to the output)
+ *                         place (router weights always applied to the output; flags as above)
  *   b200fp4_ep_combine    out[b] = sum_g parts[g][b] in fp32 (partial rows returned by the ranks)
  * ------------------------------------------------------------------------------------------- */
 B200FP4_API size_t b200fp4_ep_record_bytes(int64_t H, int64_t topk);
@@ -273,7 +288,7 @@ B200FP4_API int b200fp4_fused_sparse_moe_records(
     const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
     int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
     const float* w2_g, int64_t G2, void* out, int out_dtype, int64_t T, int64_t topk, int64_t H,
-    int64_t I, int64_t E, void* workspace, size_t workspace_bytes, void* stream);
+    int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream);
 B200FP4_API int b200fp4_ep_combine(const void* parts, int dtype, int64_t B, int64_t H, int64_t G,
                                    void* out, void* stream);
 

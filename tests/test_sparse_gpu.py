@@ -175,7 +175,8 @@ def test_ep_records_pack_fused_combine_single_gpu():
         _lib.check(L.b200fp4_fused_sparse_moe_records(recv.data_ptr(), R, _lib.BF16, emc.data_ptr(), E_glob,
                                                       *[t.data_ptr() for t in loc13], loc13[2].shape[1],
                                                       *[t.data_ptr() for t in loc2], loc2[2].shape[1],
-                                                      part.data_ptr(), _lib.BF16, G * B, topk, H, I, E, ws.data_ptr(), ws.numel(), 0), "records")
+                                                      part.data_ptr(), _lib.BF16, G * B, topk, H, I, E, _lib.SPARSE_META_ORDERED,
+                                                      ws.data_ptr(), ws.numel(), 0), "records")
         torch.cuda.synchronize()
         parts.append(part.view(G, B, H))
     for src in range(G):                                      # combine: rank src gets its block back from every rank
@@ -213,3 +214,81 @@ def test_convert_weight_batch_to_v7_matches_oracle_and_reference_golden(golden_d
     tie_free = (srt[:, :, 1] != srt[:, :, 2]).T
     np.testing.assert_array_equal(to_np(comp[0])[tie_free], gd["comp_T"][tie_free])
     np.testing.assert_array_equal(to_np(scale[0]), gd["scale_T"])
+
+
+# ---------------------------------------------------------------------------------------------
+# tensor-core path (metadata indices in increasing order, as the reference's converter writes them)
+
+_ORDERED_NIBBLES = np.array([4, 8, 12, 9, 13, 14], dtype=np.uint8)       # i0 | i1 << 2 with i0 < i1
+
+
+def _rand_sparse_ordered(E, N, K, seed, signed_scales=False):
+    rng = np.random.default_rng(seed)
+    comp = rng.integers(0, 256, (E, K // 4, N), dtype=np.uint8)
+    meta = _ORDERED_NIBBLES[rng.integers(0, 6, (E, K // 8, N))] | (_ORDERED_NIBBLES[rng.integers(0, 6, (E, K // 8, N))] << 4)
+    scale = rng.integers(1, 120, (E, K // 16, N), dtype=np.uint8)          # includes E4M3 subnormals
+    if signed_scales:
+        scale |= (rng.integers(0, 2, scale.shape, dtype=np.uint8) << 7)
+    g = (rng.random(E) * 1e-3 + 1e-4).astype(np.float32)
+    return comp, meta.astype(np.uint8), scale, g
+
+
+def test_metadata_ordered_check():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    comp, meta, scale, g = _rand_sparse_ordered(2, 128, 64, 3)
+    m = torch.from_numpy(meta).cuda()
+    assert sp7.metadata_ordered(m)
+    bad = m.clone()
+    bad[1, 3, 77] = 0x4E                                                     # low group (2, 3) ok, high group (0, 1) ok
+    assert sp7.metadata_ordered(bad)
+    bad[1, 3, 77] = 0x41                                                     # low group i0 = 1, i1 = 0
+    assert not sp7.metadata_ordered(bad)
+    bad[1, 3, 77] = 0x54                                                     # high group i0 = i1 = 1
+    assert not sp7.metadata_ordered(bad)
+
+
+@pytest.mark.parametrize("E,N,K,P,dtype", [
+    (4, 512, 128, 9, torch.float16),          # plain slab of 4 column groups, two steps per K-slice
+    (3, 1024, 2048, 17, torch.bfloat16),      # several slabs, experts with more than four tokens (two passes)
+    (5, 256, 512, 6, torch.bfloat16),         # N only allows two column groups
+    (2, 128, 1024, 5, torch.float16),         # N only allows one column group
+    (70, 512, 256, 300, torch.bfloat16),      # more items than SMs: every block walks several items
+])
+def test_batched_sparse_v7_tensor_core_path(E, N, K, P, dtype):
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    comp, meta, scale, g = _rand_sparse_ordered(E, N, K, seed=E + N + K)
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, E, P).astype(np.int32)
+    A = torch.randn(P, K, generator=torch.Generator().manual_seed(6)).to(dtype)
+    dev = _cuda(comp, meta, scale, g, ids)
+    out = sp7.batched_sparse_v7(A.cuda(), *dev, meta_ordered=True)
+    ref = oracle.batched_sparse_gemv(A.float().numpy(), comp, meta, scale, g, ids)
+    assert rel_err(to_np(out), ref) < TOL
+    general = sp7.batched_sparse_v7(A.cuda(), *dev, meta_ordered=False)
+    assert rel_err(to_np(general), ref) < TOL
+    assert torch.equal(out, sp7.batched_sparse_v7(A.cuda(), *dev))         # auto-detected, deterministic
+
+
+def test_tensor_core_path_signed_scales_and_foreign_ids():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, N, K, P = 6, 512, 256, 40
+    comp, meta, scale, g = _rand_sparse_ordered(E, N, K, seed=11, signed_scales=True)
+    ids = np.random.default_rng(2).integers(-1, E + 1, P).astype(np.int32)   # -1 and E are not local
+    A = torch.randn(P, K, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    out = to_np(sp7.batched_sparse_v7(A.cuda(), *_cuda(comp, meta, scale, g, ids), meta_ordered=True))
+    safe = np.where((ids >= 0) & (ids < E), ids, 0)
+    ref = oracle.batched_sparse_gemv(A.float().numpy(), comp, meta, scale, g, safe)
+    ref[(ids < 0) | (ids >= E)] = 0
+    assert rel_err(out, ref) < TOL
+    assert np.all(out[(ids < 0) | (ids >= E)] == 0)
+
+
+@pytest.mark.parametrize("ordered", [True, False])
+@pytest.mark.parametrize("M,topk,E,H,I", [(5, 4, 16, 512, 256), (33, 8, 24, 1024, 128), (1, 2, 8, 2048, 512)])
+def test_fused_moe_both_kernels(M, topk, E, H, I, ordered):
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    w13, w2, tw, ids, hidden = _moe_case(E, H, I, M, topk, seed=M + E)
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    out = sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), None, *c(w13), *c(w2), I, False, meta_ordered=ordered)
+    ref = _ref_fused(w13, w2, tw, ids, hidden, I)
+    assert rel_err(to_np(out), ref) < TOL

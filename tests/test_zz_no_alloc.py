@@ -39,7 +39,7 @@ def _call(L, static, A, comp, meta, scale, g, ids, dims, ws=None):
     if static:
         rc = L.b200fp4_sparse_gemv_static(*common, stream)
     else:
-        rc = L.b200fp4_sparse_gemv(*common, ws.data_ptr(), ws.numel(), stream)
+        rc = L.b200fp4_sparse_gemv(*common, 0, ws.data_ptr(), ws.numel(), stream)
     torch.cuda.synchronize()
     return rc, out
 
