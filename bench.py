@@ -234,6 +234,51 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
     return parts
 
 
+def bench_dense_nshard(dev, flush, world: int, rank: int, steps: int = 10):
+    """BASELINE configs[1] on G GPUs: the N=14336 weight split by output columns, activation replicated
+    and quantized on every rank, no exchange for the matmul; the optional all-gather of the column
+    blocks is timed separately.  Device time per call (CUDA events around 4 calls issued back to back
+    after an L2 flush), max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from dgx_vllm_b200 import synth
+    from dgx_vllm_b200.dense_shard import ColumnShardedNvfp4Linear, shard_rows
+
+    N, K = 14336, 4096
+    b, e = shard_rows(N, world, rank)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    w = (0.02 * torch.randn(N, K, generator=gen, device=dev)).to(torch.bfloat16)    # same on every rank
+    gw = synth.global_scale_of(w)
+    layer = ColumnShardedNvfp4Linear(N, gw, weight_bf16=w[b:e].contiguous())
+    del w
+    out = {}
+    reps = 4
+    for M in (128, 1024, 4096):
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+        gx = synth.global_scale_of(x)
+        res = {}
+        for gather in (False, True):
+            ts = []
+            for it in range(3 + steps):
+                flush.zero_()
+                dist.barrier()
+                a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):       # back to back, so that host launch latency is not what is timed
+                    layer.forward(x, gx, gather=gather)
+                c.record()
+                torch.cuda.synchronize()
+                if it >= 3:
+                    ts.append(a.elapsed_time(c) * 1e-3 / reps)
+            t = torch.tensor([statistics.mean(ts)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res["quant_gemm_allgather_us" if gather else "quant_gemm_us"] = float(t.item()) * 1e6
+        res["tflops_all_gpus"] = 2.0 * M * N * K / (res["quant_gemm_us"] * 1e-6) / 1e12
+        res["frac_of_nominal_fp4_peak"] = res["tflops_all_gpus"] / (9000.0 * world)
+        out[f"dense_gemm_m{M}_nshard{world}"] = res
+    return out
+
+
 def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     """BASELINE configs[3]: 8192 tokens x hidden 2048, 512 experts, Zipf(1.1)-skewed top-10 routing,
     dense NVFP4 experts (gate_up 1024x2048, down 2048x512) through the grouped path: permute ->
@@ -524,6 +569,11 @@ def main():
     e2e_val = B * world * args.steps / float(dt.item())
     sampler.end()
     clocks = sampler.stop() if rank == 0 else None
+    nshard_parts = None
+    if world > 1 and not args.no_parts and (14336 // world) % 128 == 0:
+        del w13, w2, layer
+        torch.cuda.empty_cache()
+        nshard_parts = bench_dense_nshard(dev, flush, world, rank)
     h2d = B * HIDDEN * 2 + B * TOPK * 8
     d2h = B * HIDDEN * 2
 
@@ -542,6 +592,8 @@ def main():
             line["parts"]["moe_prefill_8192_tokens"] = bench_moe_prefill(dev, flush, hbm_peak)
             torch.cuda.empty_cache()
             line["parts"]["decode_stack_48_layers"] = bench_decode_stack(dev)
+        if nshard_parts is not None:
+            line["parts"] = nshard_parts
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(B)
         print(json.dumps(line), flush=True)

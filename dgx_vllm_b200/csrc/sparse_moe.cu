@@ -725,7 +725,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
   const uint32_t off_comp = (uint32_t)t * 128u + (uint32_t)q * 16u;
   const uint32_t off_meta = 1024u + (uint32_t)(2 * (t & 1)) * 128u + (uint32_t)q * 16u + (uint32_t)(t >> 1) * 8u;
   const uint32_t off_scale = 1536u + (uint32_t)q * 16u;
-  const uint32_t off_b = (uint32_t)q * a_pitch + (uint32_t)t * 4u + (uint32_t)ks * 64u;   // token q, k = 32*ks + 2t (+8i)
+  // B column q = token q & 3 (columns 4..7 repeat the four tokens; their results are never read), k = 32*ks + 2t (+8i)
+  const uint32_t off_b = (uint32_t)(q & 3) * a_pitch + (uint32_t)t * 4u + (uint32_t)ks * 64u;
   // scratch [warp][column 0..127][token 0..3]; the 16-byte token groups of a column are XOR-swizzled
   // by the column's quad so that neither side has bank conflicts
   const uint32_t red_w = red + (uint32_t)warp * 2048u + (uint32_t)q * 256u + 8u * (uint32_t)(t & 1) +
@@ -759,11 +760,9 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
       const uint4 v0 = lds128_at(st + off_comp), v1 = lds128_at(st + off_comp + 512u);
       const uint2 m0 = lds64_at(st + off_meta), m1 = lds64_at(st + off_meta + 128u);
       const uint4 s0 = lds128_at(st + off_scale), s1 = lds128_at(st + off_scale + 128u);
-      uint32_t b[4] = {0u, 0u, 0u, 0u};
-      if (q < 4) {
+      uint32_t b[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) b[k] = lds32_at(ab + 16u * k);
-      }
+      for (int k = 0; k < 4; ++k) b[k] = lds32_at(ab + 16u * k);
       ab += 64u * KSL;
       c_st += kMmaStageBytes;
       if (c_st >= ring_end) c_st -= ring_bytes;

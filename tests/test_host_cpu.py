@@ -136,6 +136,56 @@ def test_expert_parallel_dispatch_combine_gloo_world2(tmp_path):
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
 
 
+_SHARD_WORKER = r'''
+import os, sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import numpy as np, torch, torch.distributed as dist
+import oracle
+from dgx_vllm_b200.dense_shard import ColumnShardedNvfp4Linear, shard_rows
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+M, N, K = 5, 256, 128
+g = torch.Generator().manual_seed(3)
+x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
+gx = np.float32(448.0 * 6.0 / float(x.float().abs().max())); gw = np.float32(448.0 * 6.0 / float(w.float().abs().max()))
+xb = x.view(torch.int16).numpy().view(np.uint16); wb = w.view(torch.int16).numpy().view(np.uint16)
+xc, xs = oracle.quantize_bf16(xb, gx); wc, wsf = oracle.quantize_bf16(wb, gw)
+ref = oracle.nvfp4_linear(xb, gx, wc, wsf, gw)                      # full [M, N]
+b, e = shard_rows(N, world, rank)
+def local_fn(x_, layer):                                            # CPU stand-in for quantize + GEMM: the oracle on the shard
+    return torch.from_numpy(oracle.nvfp4_linear(xb, gx, wc[layer.begin:layer.end], wsf[layer.begin:layer.end], gw)).to(torch.bfloat16)
+layer = ColumnShardedNvfp4Linear(N, torch.tensor([gw]), local_fn=local_fn)
+assert (layer.begin, layer.end) == (rank * N // world, (rank + 1) * N // world)
+part = layer.forward(x, torch.tensor([gx]))
+full = layer.forward(x, torch.tensor([gx]), gather=True)
+assert tuple(part.shape) == (M, N // world) and tuple(full.shape) == (M, N)
+err = float(np.max(np.abs(full.float().numpy() - ref)) / np.max(np.abs(ref)))
+assert err < 1e-2, err
+assert torch.equal(full[:, b:e], part)
+print(f"rank {rank} ok err={err:.3e}")
+dist.destroy_process_group()
+'''
+
+
+def test_column_sharded_linear_gloo_world2(tmp_path):
+    from dgx_vllm_b200.dense_shard import shard_rows
+    assert shard_rows(14336, 8, 3) == (5376, 7168)
+    with pytest.raises(RuntimeError):
+        shard_rows(14336, 3, 0)
+    script = tmp_path / "shard_worker.py"
+    script.write_text(_SHARD_WORKER)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
 def test_torch_custom_ops_registered_with_fake_impls():
     import dgx_vllm_b200.torch_ops  # noqa: F401
     ns = torch.ops.b200_nvfp4
