@@ -26,6 +26,12 @@ namespace b200fp4 {
 // CTA-pair (cta_group::2) kernel, gemm2.cu
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                      void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
+// gemm4.cu: 128 x 192 tiles, two accumulators (epilogue overlapped with the next tile)
+int launch_gemm_overlap(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                        void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
+// gemm3.cu: 256 x 224 tiles (two 128-row halves of A per CTA)
+int launch_gemm_tall(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                     void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
 
 namespace {
 
@@ -249,6 +255,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // (Two warps per lane quarter, each draining half of the columns, measured the same on B200:
+    // 154.7 vs 153 us at M=4096, N=14336, K=4096.)
     const int quarter = warp & 3;                 // tensor-memory lanes [32*quarter, +32) belong to this warp
     const float alpha_dense = kGrouped ? 0.f : p.alpha[0];
     uint32_t tcount = 0;
@@ -554,7 +562,7 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
       ((K / 2) % 16) != 0)
     return B200FP4_STATUS_INVALID_VALUE;
   if (!workspace || workspace_bytes < 256 || !aligned(workspace, 16)) return B200FP4_STATUS_ALLOC_FAILED;
-  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 512) return B200FP4_STATUS_INVALID_VALUE;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 224 && tile_n != 192 && tile_n != 512) return B200FP4_STATUS_INVALID_VALUE;
   if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24)) return B200FP4_STATUS_NOT_SUPPORTED;
   if (b200fp4_has_hardware_acceleration() != 1) return B200FP4_STATUS_ARCH_MISMATCH;
   cudaStream_t st = (cudaStream_t)stream;
@@ -575,6 +583,24 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   if (cudaMemsetAsync(workspace, 0, 16, st) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  if (bn == 192) {
+    CUtensorMap pa, pb;
+    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 128, 128) ||
+        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 192, 128))
+      return B200FP4_STATUS_INTERNAL_ERROR;
+    int rc4 = launch_gemm_overlap(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
+    if (rc4 != B200FP4_STATUS_SUCCESS) return rc4;
+    return finish_launch(2);
+  }
+  if (bn == 224) {
+    CUtensorMap pa, pb;
+    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 256, 128) ||
+        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 224, 128))
+      return B200FP4_STATUS_INTERNAL_ERROR;
+    int rc3 = launch_gemm_tall(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
+    if (rc3 != B200FP4_STATUS_SUCCESS) return rc3;
+    return finish_launch(2);
   }
   if (bn == 512) {
     // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)

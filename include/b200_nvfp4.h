@@ -106,7 +106,9 @@ B200FP4_API int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M,
  *             (b200fp4_sf_swizzled_bytes(rows, K/16) bytes each)
  *   alpha     device pointer to one f32 (= 1 / (global_scale_a * global_scale_b))
  *   out       [M, N] bf16 or f16
- *   tile_n    0 = choose; 128 or 256 forces the CTA tile width; 512 selects the two-CTA kernel
+ *   tile_n    0 = choose; 128 or 256 forces the CTA tile width of the 128-row kernel; 192 selects the
+ *             128 x 192 kernel with two accumulators (epilogue overlapped with the next tile); 224 the
+ *             256 x 224 kernel (two 128-row halves of A per CTA); 512 selects the two-CTA kernel
  *             (a cluster of two SMs shares one 256x256 tile through tcgen05 cta_group::2) -- an
  *             opt-in variant that is never chosen automatically: it measured slower than the
  *             256-wide single-CTA kernel (260 us against 150 us at M=4096, N=14336, K=4096)
