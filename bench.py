@@ -279,6 +279,60 @@ def bench_dense_nshard(dev, flush, world: int, rank: int, steps: int = 10):
     return out
 
 
+def _dense_experts(dev, gen, E, N, K):
+    """E dense NVFP4 expert matrices [N,K]: (codes [E,N,K/2], swizzled scales, global scales [E])."""
+    import torch
+    from dgx_vllm_b200 import scaled_fp4_quant, synth
+    codes = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
+    sf = torch.empty(E, (N + 127) // 128 * 128, (K // 16 + 3) // 4 * 4, dtype=torch.uint8, device=dev)
+    gs = torch.empty(E, dtype=torch.float32, device=dev)
+    for e0 in range(0, E, 64):
+        n = min(64, E - e0)
+        w = (0.02 * torch.randn(n, N, K, generator=gen, device=dev)).to(torch.bfloat16)
+        for i in range(n):
+            g = synth.global_scale_of(w[i])
+            c, s_ = scaled_fp4_quant(w[i], g)
+            codes[e0 + i], sf[e0 + i], gs[e0 + i] = c, s_.view(torch.uint8), g[0]
+    return codes, sf, gs
+
+
+def bench_moe_prefill_ep(dev, flush, world: int, rank: int, steps: int = 5):
+    """BASELINE configs[3] expert-parallel: 8192 tokens in blocks of 8192/G per rank, 512/G experts per
+    rank; all-gather of the token blocks, grouped NVFP4 path over the local experts, reduce-scatter of
+    the fp32 partial rows.  Device time per layer, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from dgx_vllm_b200 import synth
+    from dgx_vllm_b200.moe_ep import ExpertParallelMoEPrefill
+
+    T, E, H, I, topk = 8192, 512, 2048, 512, 10
+    El, Tl = E // world, T // world
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    w13c, w13s, w13g = _dense_experts(dev, gen, El, 2 * I, H)
+    w2c, w2s, w2g = _dense_experts(dev, gen, El, H, I)
+    hidden = synth.make_hidden(Tl, H, 5 + rank, dev)
+    tw, ids = synth.make_routing(Tl, E, topk, 6 + rank, dev, zipf=1.1)
+    a1 = torch.full((El,), 448.0 * 6.0 / 6.0, dtype=torch.float32, device=dev)      # |N(0,1)| < 6 for these inputs
+    a2 = torch.full((El,), 448.0 * 6.0 / 2.0, dtype=torch.float32, device=dev)
+    layer = ExpertParallelMoEPrefill(E, (w13c, w13s, w13g, w2c, w2s, w2g, a1, a2))
+    ts = []
+    for it in range(3 + steps):
+        flush.zero_()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        layer.forward(hidden, tw, ids)
+        b.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            ts.append(a.elapsed_time(b) * 1e-3)
+    t = torch.tensor([statistics.mean(ts)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t = float(t.item())
+    return {"tokens_per_s": T / t, "ms": t * 1e3, "tflops_all_gpus": 2.0 * T * topk * (2 * I * H + H * I) / t / 1e12,
+            "config": f"8192 tokens ({Tl} per rank), 512 experts ({El} per rank), Zipf(1.1) top-10, all-gather + grouped path + reduce-scatter"}
+
+
 def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     """BASELINE configs[3]: 8192 tokens x hidden 2048, 512 experts, Zipf(1.1)-skewed top-10 routing,
     dense NVFP4 experts (gate_up 1024x2048, down 2048x512) through the grouped path: permute ->
@@ -291,20 +345,8 @@ def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     T, E, H, I, topk = 8192, 512, 2048, 512, 10
     gen = torch.Generator(device=dev).manual_seed(11)
 
-    def experts(N, K):
-        codes = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
-        sf = torch.empty(E, (N + 127) // 128 * 128, (K // 16 + 3) // 4 * 4, dtype=torch.uint8, device=dev)
-        gs = torch.empty(E, dtype=torch.float32, device=dev)
-        for e0 in range(0, E, 64):
-            w = (0.02 * torch.randn(64, N, K, generator=gen, device=dev)).to(torch.bfloat16)
-            for i in range(64):
-                g = synth.global_scale_of(w[i])
-                c, s_ = scaled_fp4_quant(w[i], g)
-                codes[e0 + i], sf[e0 + i], gs[e0 + i] = c, s_.view(torch.uint8), g[0]
-        return codes, sf, gs
-
-    w13c, w13s, w13g = experts(2 * I, H)
-    w2c, w2s, w2g = experts(H, I)
+    w13c, w13s, w13g = _dense_experts(dev, gen, E, 2 * I, H)
+    w2c, w2s, w2g = _dense_experts(dev, gen, E, H, I)
     hidden = synth.make_hidden(T, H, 5, dev)
     tw, ids = synth.make_routing(T, E, topk, 6, dev, zipf=1.1)
     a1 = (448.0 * 6.0 / hidden.float().abs().max()).repeat(E).float()
@@ -574,6 +616,8 @@ def main():
         del w13, w2, layer
         torch.cuda.empty_cache()
         nshard_parts = bench_dense_nshard(dev, flush, world, rank)
+        torch.cuda.empty_cache()
+        nshard_parts[f"moe_prefill_8192_tokens_ep{world}"] = bench_moe_prefill_ep(dev, flush, world, rank)
     h2d = B * HIDDEN * 2 + B * TOPK * 8
     d2h = B * HIDDEN * 2
 

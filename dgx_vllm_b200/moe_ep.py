@@ -1,5 +1,10 @@
-"""Expert-parallel MoE decode layer: E/G experts per GPU, token dispatch and combine with one
-all-to-all each way over NCCL (NVLink / NVSwitch), local compute by the fused sparse MoE op.
+"""Expert-parallel MoE layers: E/G experts per GPU.
+
+Decode (`ExpertParallelMoE`): token dispatch and combine with one all-to-all each way over NCCL
+(NVLink / NVSwitch), local compute by the fused sparse MoE op.
+Prefill (`ExpertParallelMoEPrefill`): with thousands of tokens and top-10 of 512 experts nearly every
+token has an expert on every rank, so dispatch is an all-gather of the token block and combine a
+reduce-scatter of the partial output rows; local compute is the grouped NVFP4 path.
 
 The reference has no multi-GPU code of its own (it serves with tensor parallelism through vLLM);
 this layout is the one the path's shard rule prescribes: experts [r*E/G, (r+1)*E/G) live on rank r.
@@ -147,3 +152,58 @@ class ExpertParallelMoE:
         if self._fn is not None:
             return self._forward_torch(hidden, topk_w, topk_ids, emap)
         return self._forward_cuda(hidden, topk_w, topk_ids, emap)
+
+
+class ExpertParallelMoEPrefill:
+    """One dense-NVFP4 MoE layer for prefill, experts sharded over the ranks of `group`.
+
+    Every rank holds a block of Tl tokens and the weights of its E/G experts (the arguments of
+    `grouped_moe.nvfp4_moe_prefill` for those experts).  forward: all-gather (tokens, router weights,
+    ids) -> grouped path over the local experts with `expert_map` masking the others (pairs of foreign
+    experts contribute nothing) -> reduce-scatter of the fp32 partial rows -> [Tl, H].
+
+    `local_fn(hidden [T,H], topk_w [T,k], topk_ids [T,k], expert_map [global_E]) -> [T,H]`, when given,
+    replaces the CUDA path (CPU ranks in tests; gloo has no reduce-scatter, so an all-reduce + slice
+    stands in for it there)."""
+
+    def __init__(self, global_E: int, weights: Optional[tuple], group=None, local_fn: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if global_E % self.world != 0:
+            raise RuntimeError("the number of experts must be divisible by the number of ranks")
+        self.global_E = global_E
+        self.weights = weights       # (w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs, a1_gs, a2_gs) of the local experts
+        self._fn = local_fn
+        self._emap = None
+
+    def _local(self, hidden, topk_w, topk_ids, emap):
+        if self._fn is not None:
+            return self._fn(hidden, topk_w, topk_ids, emap)
+        from .grouped_moe import nvfp4_moe_prefill
+        return nvfp4_moe_prefill(hidden, topk_w, topk_ids, *self.weights, expert_map=emap)
+
+    def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        if self._emap is None or self._emap.device != hidden.device:
+            self._emap = expert_map_for_rank(self.global_E, self.world, self.rank, hidden.device)
+        G = self.world
+        if G == 1:
+            return self._local(hidden, topk_w, topk_ids, self._emap)
+        Tl, H = hidden.shape
+        k = topk_ids.shape[1]
+        ids = topk_ids.to(torch.int32).contiguous()
+        tw = topk_w.to(torch.float32).contiguous()
+        h_all = torch.empty((G * Tl, H), dtype=hidden.dtype, device=hidden.device)
+        w_all = torch.empty((G * Tl, k), dtype=torch.float32, device=hidden.device)
+        i_all = torch.empty((G * Tl, k), dtype=torch.int32, device=hidden.device)
+        dist.all_gather_into_tensor(h_all, hidden.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(w_all, tw, group=self.group)
+        dist.all_gather_into_tensor(i_all, ids, group=self.group)
+        part = self._local(h_all, w_all, i_all, self._emap).float().contiguous()     # [G*Tl, H] partial rows
+        if dist.get_backend(self.group) == "gloo":
+            dist.all_reduce(part, group=self.group)
+            out = part[self.rank * Tl:(self.rank + 1) * Tl]
+        else:
+            out = torch.empty((Tl, H), dtype=torch.float32, device=hidden.device)
+            dist.reduce_scatter_tensor(out, part, group=self.group)
+        return out.to(hidden.dtype)

@@ -186,6 +186,54 @@ def test_column_sharded_linear_gloo_world2(tmp_path):
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
 
 
+_PREFILL_WORKER = r'''
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+from dgx_vllm_b200.moe_ep import ExpertParallelMoEPrefill
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+E, H, Tl, k = 8, 16, 5, 3
+def expert_fn(e, h):                                   # a stand-in expert: scale by (e + 1)
+    return (e + 1.0) * h
+def local_fn(hidden, tw, ids, emap):                   # contributions of the experts this rank owns
+    out = torch.zeros(hidden.shape, dtype=torch.float32)
+    for t in range(hidden.shape[0]):
+        for j in range(ids.shape[1]):
+            if int(emap[int(ids[t, j])]) >= 0:
+                out[t] += tw[t, j] * expert_fn(float(ids[t, j]), hidden[t].float())
+    return out
+g = torch.Generator().manual_seed(100 + rank)
+hidden = torch.randn(Tl, H, generator=g)
+ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(Tl)]).to(torch.int32)
+tw = torch.rand(Tl, k, generator=g)
+layer = ExpertParallelMoEPrefill(E, None, local_fn=local_fn)
+out = layer.forward(hidden, tw, ids)
+ref = torch.zeros(Tl, H)
+for t in range(Tl):
+    for j in range(k):
+        ref[t] += tw[t, j] * expert_fn(float(ids[t, j]), hidden[t])
+assert tuple(out.shape) == (Tl, H)
+assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5), float((out - ref).abs().max())
+print(f"rank {rank} ok")
+dist.destroy_process_group()
+'''
+
+
+def test_expert_parallel_prefill_gloo_world2(tmp_path):
+    script = tmp_path / "prefill_worker.py"
+    script.write_text(_PREFILL_WORKER)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), ROOT],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout
+
+
 def test_torch_custom_ops_registered_with_fake_impls():
     import dgx_vllm_b200.torch_ops  # noqa: F401
     ns = torch.ops.b200_nvfp4
