@@ -1003,12 +1003,18 @@ size_t mma_smem_bytes(int64_t K, int stages) {
   return 1024 + a_bytes + kMmaRedBytes + (size_t)kMmaWarps * stages * kMmaStageBytes;
 }
 
-MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu) {
+// `passes` is an upper bound of the number of passes (the real number is only known on the device).
+// Wide items (more column groups) have less per-item work to amortise, but with few passes they leave
+// SMs without an item, so small batches take the narrowest shape that is allowed.
+MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu, int64_t passes) {
   MmaCfg c = {0, 0, false};
   if (G != K / 16 || K % 32 != 0) return c;
   const int order_silu[3] = {2, 4, 1}, order_plain[3] = {4, 2, 1};
+  const int order_small[3] = {1, 2, 4};
+  const int64_t slabs_wide = inter_silu > 0 ? inter_silu / 128 : N / 512;     // slabs per pass of the preferred wide shape
+  const bool small = passes * (slabs_wide > 0 ? slabs_wide : 1) < 2 * (int64_t)sm_count();
   for (int i = 0; i < 3; ++i) {
-    const int cg = inter_silu > 0 ? order_silu[i] : order_plain[i];
+    const int cg = small ? order_small[i] : (inter_silu > 0 ? order_silu[i] : order_plain[i]);
     const int ksl = kMmaWarps / cg;
     const bool cols_ok = inter_silu > 0 ? (inter_silu % (64 * cg) == 0 && N == 2 * (int64_t)inter_silu) : (N % (128 * cg) == 0);
     if (cols_ok && K % (32 * ksl) == 0 && K / (32 * ksl) >= 2) {
@@ -1125,7 +1131,7 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
   const bool s8 = (G == K / 8);
   if (meta_ordered) {
     // tensor-core kernel where the shape allows it (one scale per 16 k, whole 128-column groups)
-    const MmaCfg mc = pick_mma_cfg(N, K, G, inter_silu);
+    const MmaCfg mc = pick_mma_cfg(N, K, G, inter_silu, P < E ? P : E);
     if (mc.ok) {
       g.n_slabs = inter_silu > 0 ? inter_silu / (64 * mc.cg) : (int)(N / (128 * mc.cg));
       int64_t grid = max_passes(P, E) * g.n_slabs;

@@ -67,7 +67,7 @@ def quantize_weight(U, w: torch.Tensor):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of Avarok-Cybersecurity/dgx-vllm")
     args = ap.parse_args()
     U, run_emul = load_reference_emulation(args.reference)
     S = load_reference_sparse(args.reference)
