@@ -74,12 +74,14 @@ class ExpertParallelMoE:
         self._fn = local_moe_fn
         self._bufs = {}
         self._flags = None
+        self._bound = None
 
     def _cuda_local(self, hidden, topk_w, topk_ids, emap):
-        from . import sparse_fp4_v7 as sp7
-        k = ("comp_T", "meta_T", "scale_T", "g_scales")
-        return sp7.fused_sparse_moe_v7(hidden, topk_w, topk_ids, emap, *[self.w13[x] for x in k],
-                                       *[self.w2[x] for x in k], self.inter, False)
+        if self._bound is None:       # weights are validated and their pointers bound once
+            from . import sparse_fp4_v7 as sp7
+            k = ("comp_T", "meta_T", "scale_T", "g_scales")
+            self._bound = sp7.FusedSparseMoE(*[self.w13[x] for x in k], *[self.w2[x] for x in k], self.inter, expert_map=emap)
+        return self._bound(hidden, topk_w, topk_ids)
 
     def expert_map(self, device) -> torch.Tensor:
         if self._emap is None or self._emap.device != device:

@@ -213,6 +213,75 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
     return out
 
 
+class FusedSparseMoE:
+    """`fused_sparse_moe_v7` with the weight arguments bound once.
+
+    A serving layer calls the op with the same eight weight tensors (and expert_map) every step;
+    validating them, testing the metadata order and converting 20 pointers per call costs more host
+    time than the kernels need for a small batch.  This object does that work once and keeps
+    per-call work to the three activation-side tensors.  Results are identical to the function's."""
+
+    def __init__(self, w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales,
+                 inter_size: int, expert_map=None, meta_ordered=None):
+        dev = require_cuda(w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales)
+        for t, n in ((w13_comp, "w13_comp"), (w13_meta, "w13_meta"), (w13_scale, "w13_scale"), (w2_comp, "w2_comp"),
+                     (w2_meta, "w2_meta"), (w2_scale, "w2_scale")):
+            _check_u8(t, n)
+        E, H4, I2 = w13_comp.shape
+        self.E, self.H, self.I = E, H4 * 4, int(inter_size)
+        H, I = self.H, self.I
+        require(I2 == 2 * I, "w13_comp must be [E, H/4, 2I]")
+        require(tuple(w13_meta.shape) == (E, H // 8, 2 * I), "w13_meta must be [E, H/8, 2I]")
+        require(w13_scale.shape[0] == E and w13_scale.shape[2] == 2 * I, "w13_scale must be [E, G, 2I]")
+        require(tuple(w2_comp.shape) == (E, I // 4, H), "w2_comp must be [E, I/4, H]")
+        require(tuple(w2_meta.shape) == (E, I // 8, H), "w2_meta must be [E, I/8, H]")
+        require(w2_scale.shape[0] == E and w2_scale.shape[2] == H, "w2_scale must be [E, G, H]")
+        for g in (w13_g_scales, w2_g_scales):
+            require(g.dtype == torch.float32 and g.numel() >= E and g.is_contiguous(), "g_scales must be f32 [E]")
+        emap = None
+        if expert_map is not None and expert_map.numel() > 0:
+            require(expert_map.is_cuda, "expert_map must be a CUDA tensor")
+            emap = (expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)).contiguous()
+        self.device = dev
+        self._keep = (w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales, emap)
+        self._flags = _flags(meta_ordered, w13_meta, w2_meta)
+        self._head = (ptr(emap), 0 if emap is None else emap.numel(),
+                      ptr(w13_comp), ptr(w13_meta), ptr(w13_scale), ptr(w13_g_scales), w13_scale.shape[1],
+                      ptr(w2_comp), ptr(w2_meta), ptr(w2_scale), ptr(w2_g_scales), w2_scale.shape[1])
+        self._lib = _lib.lib()
+        self._fn = self._lib.b200fp4_fused_sparse_moe
+        self._ws_bytes = {}
+
+    def __call__(self, hidden_states, topk_weights, topk_ids, apply_router_weight_on_input: bool = False, out=None):
+        M, H = hidden_states.shape
+        topk = topk_ids.shape[1]
+        require(hidden_states.is_cuda and H == self.H and hidden_states.is_contiguous() and
+                hidden_states.dtype in (torch.float16, torch.bfloat16), "hidden_states must be a contiguous [M,H] 16-bit CUDA tensor")
+        tw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+        ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        require(tw.is_contiguous() and ids.is_contiguous() and tuple(tw.shape) == (M, topk) and ids.shape[0] == M,
+                "topk_weights / topk_ids must be contiguous [M, topk]")
+        dev = self.device
+        if out is None:
+            out = torch.empty((M, H), dtype=hidden_states.dtype, device=dev)
+        key = (M, topk)
+        nws = self._ws_bytes.get(key)
+        if nws is None:
+            nws = self._ws_bytes[key] = self._lib.b200fp4_fused_moe_workspace_bytes(M, topk, H, self.I, self.E)
+        ws = workspace(dev, nws)
+        code = dtype_code(hidden_states.dtype)
+        flags = self._flags | (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0)
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                rc = self._fn(hidden_states.data_ptr(), code, tw.data_ptr(), ids.data_ptr(), *self._head, out.data_ptr(),
+                              dtype_code(out.dtype), M, topk, H, self.I, self.E, flags, ws.data_ptr(), ws.numel(), stream_ptr(dev))
+        else:
+            rc = self._fn(hidden_states.data_ptr(), code, tw.data_ptr(), ids.data_ptr(), *self._head, out.data_ptr(),
+                          dtype_code(out.dtype), M, topk, H, self.I, self.E, flags, ws.data_ptr(), ws.numel(), stream_ptr(dev))
+        _lib.check(rc, "fused_sparse_moe_v7")
+        return out
+
+
 def convert_weight_batch_to_v7(weights, scales, g_scales, device="cuda", batch_size=16):
     """NVFP4 expert weights -> the 2:4 tensors the ops above take, on the GPU in two launches.
 

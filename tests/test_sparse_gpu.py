@@ -292,3 +292,21 @@ def test_fused_moe_both_kernels(M, topk, E, H, I, ordered):
     out = sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), None, *c(w13), *c(w2), I, False, meta_ordered=ordered)
     ref = _ref_fused(w13, w2, tw, ids, hidden, I)
     assert rel_err(to_np(out), ref) < TOL
+
+
+def test_bound_layer_object_matches_function():
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, H, I, B, topk = 16, 1024, 256, 9, 4
+    w13, w2, tw, ids, hidden = _moe_case(E, H, I, B, topk, seed=77)
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    a13, a2 = c(w13), c(w2)
+    emap = torch.arange(E, dtype=torch.int32)
+    emap[::3] = -1
+    emap = emap.cuda()
+    layer = sp7.FusedSparseMoE(*a13, *a2, I, expert_map=emap)
+    for on_input in (False, True):
+        ref = sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), emap, *a13, *a2, I, on_input)
+        out = layer(hidden.cuda(), tw.cuda(), ids.cuda(), apply_router_weight_on_input=on_input)
+        assert torch.equal(out, ref)
+    with pytest.raises(RuntimeError):
+        layer(hidden.cuda()[:, :512].contiguous(), tw.cuda(), ids.cuda())
