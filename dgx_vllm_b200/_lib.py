@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libb200nvfp4.so")
 
 F16, BF16, F32 = 0, 1, 2
-MOE_ROUTER_WEIGHT_ON_INPUT, SPARSE_META_ORDERED = 1, 2     # flags of the sparse entry points
+MOE_ROUTER_WEIGHT_ON_INPUT, SPARSE_META_ORDERED, MOE_SEPARATE_LAUNCHES = 1, 2, 4     # flags of the sparse entry points
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64

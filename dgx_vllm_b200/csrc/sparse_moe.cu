@@ -76,7 +76,8 @@ struct GemvArgs {
 __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
                     Plan plan, const __nv_bfloat16* __restrict__ conv_src, __half* __restrict__ conv_dst,
-                    int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks) {
+                    int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks,
+                    int* zero_buf, int zero_count) {
   if (blockIdx.x > 0) {
     const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
     for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
@@ -95,6 +96,8 @@ __global__ void __launch_bounds__(kPlanThreads)
   __shared__ int s_warp[3][32];
   const int tid = threadIdx.x;
   for (int e = tid; e < E; e += kPlanThreads) s_count[e] = 0;
+  for (int i = tid; i < zero_count; i += kPlanThreads) zero_buf[i] = 0;   // per-pass counters of the one-launch layer
+  if (tid == 0) plan.hdr[3] = 0;
   __syncthreads();
   for (int p = tid; p < P; p += kPlanThreads) {
     int e = ids[(int64_t)(p / ids_topk) * ids_ld + (p % ids_topk)];   // ids rows may be strided
@@ -628,12 +631,14 @@ __device__ __forceinline__ __half2 e4m3x2_to_h2(uint32_t w) {
   return as_h2(r);
 }
 
-template <int CG, int S, bool kSilu>
-__global__ void __launch_bounds__(kMmaThreads, 1)
-    sparse_gemv_mma_kernel(const GemvArgs g) {
+// One projection over all items of this block.  kDep links the two projections of the MoE layer when
+// they run in one launch: 1 = producer (done[pass] is incremented once an item's output is stored and
+// fenced), 2 = consumer (the activations of a pass are staged only after done[pass] has reached
+// `need` = producer slabs per pass), 0 = stand-alone.
+template <int CG, int S, bool kSilu, int kDep>
+__device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char* smem, int* done, int need) {
   constexpr int KSL = kMmaWarps / CG;          // K-slices per item
   constexpr int VCOLS = 128 * CG;              // columns of a slab (SiLU: 64*CG gate + 64*CG up)
-  extern __shared__ __align__(16) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int q = lane >> 2, t = lane & 3;
   const int cgw = warp % CG, ks = warp / CG;
@@ -716,6 +721,38 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     if (f_dst >= ring_end) f_dst -= ring_bytes;
   };
 
+  // consumer side of the dependency: thread 0 reads a pass's counter (acquire) one item ahead, so the
+  // load's latency is hidden; only a counter that is still short is polled (bounded), and the block's
+  // next barrier releases the other threads
+  auto load_count = [&](int pass) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(done + pass) : "memory");
+    return v;
+  };
+  auto wait_pass = [&](int pass, int seen) {
+    if (kDep == 2 && tid == 0 && pass >= 0 && seen < need) {
+      const long long t0 = clock64();
+      while (load_count(pass) < need) {
+        if (clock64() - t0 > 2000000000LL) {   // ~1 s: give up, flag it, carry on (results of this pass are then wrong)
+          g.plan.hdr[3] = -1;
+          break;
+        }
+      }
+    }
+  };
+  // producer side: an item's output is complete for the whole block at the next block-wide barrier;
+  // thread 0 then fences (cumulative over the barrier) and counts the item
+  int finished_pass = -1;
+  auto signal_finished = [&]() {
+    if (kDep == 1 && tid == 0 && finished_pass >= 0) {
+      __threadfence();
+      atomicAdd(done + finished_pass, 1);
+    }
+  };
+  int seen_next = 0;      // thread 0: counter of the next item's pass, read during the previous item
+  wait_pass(pass_of(0), 0);
+  if (kDep == 2) __syncthreads();
+  if (kDep == 2 && tid == 0 && my_items > 1) seen_next = load_count(pass_of(1));
   issue_A(rc, 0);
   cp_async_commit();
 #pragma unroll
@@ -743,8 +780,11 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
     if (nstep >= S - 1) cp_async_wait<S - 2>();
     else if (nstep == 2) cp_async_wait<1>();
     else cp_async_wait<(S > 3 ? 2 : 1)>();
+    wait_pass(i_cur + 1 < my_items ? pass_of(i_cur + 1) : -1, seen_next);
     __syncthreads();   // activations of this pass complete for all threads; scratch and the other buffer free
+    signal_finished();
     issue_A(rn, abuf ^ 1);   // rides on the next committed weight stage
+    if (kDep == 2 && tid == 0 && i_cur + 2 < my_items) seen_next = load_count(pass_of(i_cur + 2));
 
     float acc[8][4];
 #pragma unroll
@@ -838,12 +878,37 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
         if (tok < rc.nt) store_out(g.out, g.out_dtype, (int64_t)rc.pair(tok) * g.ldo + slab * VCOLS + v, sum * gmul);
       }
     }
+    if (kDep == 1) finished_pass = pass_of(i_cur);   // counted after the next block-wide barrier
     rc = rn;
     rn = rnn;
     e_nn = e_n3;
     abuf ^= 1;
   }
   cp_async_wait<0>();
+  if (kDep == 1) {
+    __syncthreads();
+    signal_finished();
+  }
+}
+
+template <int CG, int S, bool kSilu>
+__global__ void __launch_bounds__(kMmaThreads, 1) sparse_gemv_mma_kernel(const GemvArgs g) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  gemv_mma_phase<CG, S, kSilu, 0>(g, smem, nullptr, 0);
+}
+
+// Both projections of the MoE layer in one launch: every block first walks its gate_up items, then its
+// down items.  A down item only needs the activations of its own pass, so blocks that run out of
+// gate_up items start on the down projection of passes finished long ago instead of idling through
+// the last, partial round and a second kernel's ramp-up.  Launched cooperatively (all blocks
+// co-resident), so a block polling for a pass can never keep the block that produces it off the GPU.
+template <int CGA, int SA, int CGB, int SB>
+__global__ void __launch_bounds__(kMmaThreads, 1)
+    fused_moe_mma_kernel(const GemvArgs ga, const GemvArgs gb, int* done, int need) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  gemv_mma_phase<CGA, SA, true, 1>(ga, smem, done, need);
+  __syncthreads();              // the second phase lays shared memory out anew
+  gemv_mma_phase<CGB, SB, false, 2>(gb, smem, done, need);
 }
 
 // ------------------------------------------------------------------------------------------ generic
@@ -1097,7 +1162,7 @@ int check_common(const void* A, int a_dtype, const void* out, int out_dtype, int
 // Plan + (for bf16 activations) conversion to fp16 in one launch.
 void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld, const int32_t* expert_map,
                  int64_t global_E, int64_t E, const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_rows,
-                 int64_t a_cols, int64_t a_ld, cudaStream_t st) {
+                 int64_t a_cols, int64_t a_ld, cudaStream_t st, int* zero_buf = nullptr, int zero_count = 0) {
   int64_t chunks = 0;
   unsigned blocks = 1;
   if (a_bf16 != nullptr) {
@@ -1108,13 +1173,13 @@ void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld
   }
   moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan,
                                                    reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks,
-                                                   (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8);
+                                                   (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8, zero_buf,
+                                                   zero_count);
 }
 
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
-int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
-                   int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int inter_silu,
-                   bool meta_ordered, cudaStream_t st) {
+GemvArgs make_args(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
+                   int out_dtype, int64_t ldo, int64_t N, int64_t K, int inter_silu) {
   GemvArgs g;
   g.w = w;
   g.plan = plan;
@@ -1128,6 +1193,49 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
   g.N = (int)N;
   g.K = (int)K;
   g.inter = inter_silu;
+  g.n_slabs = 1;
+  return g;
+}
+
+// Both projections of the layer in one cooperative launch (tensor-core kernel).  Returns
+// NOT_SUPPORTED when the shapes do not map to one of the instantiated pairs of configurations or the
+// device cannot keep all blocks resident; the caller then launches the projections one by one.
+template <int CGA, int CGB>
+int launch_fused_pair(GemvArgs ga, GemvArgs gb, int* done, int64_t P, int64_t E, cudaStream_t st) {
+  const void* fn = reinterpret_cast<const void*>(&fused_moe_mma_kernel<CGA, 5, CGB, 5>);
+  const size_t smem = mma_smem_bytes(ga.K, 5) > mma_smem_bytes(gb.K, 5) ? mma_smem_bytes(ga.K, 5) : mma_smem_bytes(gb.K, 5);
+  static int state[64] = {0};     // per device: 0 unknown, 1 usable, -1 not usable
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (state[dev] == 0) {
+    int coop = 0, per_sm = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    bool ok = coop != 0 && cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess &&
+              cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kMmaThreads, 227 * 1024) == cudaSuccess && per_sm >= 1;
+    if (!ok) cudaGetLastError();
+    state[dev] = ok ? 1 : -1;
+  }
+  if (state[dev] < 0) return B200FP4_STATUS_NOT_SUPPORTED;
+  ga.n_slabs = ga.inter / (64 * CGA);
+  gb.n_slabs = gb.N / (128 * CGB);
+  int need = ga.n_slabs;
+  const int64_t slabs = ga.n_slabs > gb.n_slabs ? ga.n_slabs : gb.n_slabs;
+  int64_t grid = max_passes(P, E) * slabs;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  if (grid < 1) grid = 1;
+  void* args[4] = {&ga, &gb, &done, &need};
+  if (cudaLaunchCooperativeKernel(fn, dim3((unsigned)grid), dim3(kMmaThreads), args, smem, st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_NOT_SUPPORTED;
+  }
+  return B200FP4_STATUS_SUCCESS;
+}
+
+int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
+                   int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int inter_silu,
+                   bool meta_ordered, cudaStream_t st) {
+  GemvArgs g = make_args(w, plan, A, lda, a_div, out, out_dtype, ldo, N, K, inter_silu);
   const bool s8 = (G == K / 8);
   if (meta_ordered) {
     // tensor-core kernel where the shape allows it (one scale per 16 k, whole 128-column groups)
@@ -1321,7 +1429,8 @@ extern "C" size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
   const int64_t P = M * topk;
   return align_up(plan_bytes(P, E), 256) + align_up((size_t)M * H * sizeof(__half), 256) +
-         align_up((size_t)P * I * sizeof(__half), 256) + align_up((size_t)P * H * sizeof(float), 256);
+         align_up((size_t)P * I * sizeof(__half), 256) + align_up((size_t)P * H * sizeof(float), 256) +
+         align_up((size_t)max_passes(P, E) * sizeof(int), 256);
 }
 
 // ld_h / ld_w / ld_ids: row strides (in elements) of hidden, topk_weights and topk_ids.
@@ -1367,9 +1476,34 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   float* down = reinterpret_cast<float*>(ws + off);
   const bool bf = h_dtype == B200FP4_DTYPE_BF16;
   const bool ordered = (flags & B200FP4_SPARSE_META_ORDERED) != 0;
+  off += align_up((size_t)P * H * sizeof(float), 256);
+  int* done = reinterpret_cast<int*>(ws + off);
+  const int64_t n_done = max_passes(P, E);
 
-  launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M, H, ld_h, st);
+  launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M, H, ld_h, st, done,
+              (int)n_done);
   if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
+  if (ordered && !(flags & B200FP4_MOE_SEPARATE_LAUNCHES)) {
+    // one cooperative launch for both projections when both take the tensor-core kernel with five ring stages
+    const int64_t pb = P < E ? P : E;
+    const MmaCfg ca = pick_mma_cfg(2 * I, H, G13, (int)I, pb), cb = pick_mma_cfg(H, I, G2, 0, pb);
+    if (ca.ok && cb.ok && ca.stages == 5 && cb.stages == 5) {
+      const GemvArgs ga = make_args(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk,
+                                    act, B200FP4_DTYPE_F16, I, 2 * I, H, (int)I);
+      const GemvArgs gb = make_args(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, H, I, 0);
+      int frc = B200FP4_STATUS_NOT_SUPPORTED;
+      if (ca.cg == 2 && cb.cg == 4) frc = launch_fused_pair<2, 4>(ga, gb, done, P, E, st);
+      else if (ca.cg == 1 && cb.cg == 2) frc = launch_fused_pair<1, 2>(ga, gb, done, P, E, st);
+      if (frc == B200FP4_STATUS_SUCCESS) {
+        if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
+        if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
+        dim3 grid1((unsigned)((H + 255) / 256), (unsigned)M);
+        weighted_reduce_kernel<<<grid1, 256, 0, st>>>(down, topk_weights, plan.mapped, out, out_dtype, (int)M, (int)topk,
+                                                      (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
+        return finish_launch(3);
+      }
+    }
+  }
   rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk, act,
                       B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, ordered, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;

@@ -161,13 +161,16 @@ def batched_sparse_packed_v7(A, B_packed_T, g_scales, expert_ids, orig_K, *, out
 def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
                         w13_comp, w13_meta, w13_scale, w13_g_scales,
                         w2_comp, w2_meta, w2_scale, w2_g_scales,
-                        inter_size, apply_router_weight_on_input, *, out_dtype=None, meta_ordered=None):
+                        inter_size, apply_router_weight_on_input, *, out_dtype=None, meta_ordered=None,
+                        separate_launches=False):
     """One MoE layer for decode (fused_sparse_moe_v7, sparse_fp4_v7.cu:607-742):
     gate_up GEMV -> SiLU(gate)*up -> down GEMV -> router-weighted sum.
 
     hidden_states [M,H] f16/bf16; topk_weights [M,topk] f32; topk_ids [M,topk] int; expert_map [global_E]
     int32 or an empty tensor / None for identity; w13_* [E,H/4,2I], [E,H/8,2I], [E,G,2I], [E];
-    w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H].  meta_ordered as in batched_sparse_v7."""
+    w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H].  meta_ordered as in batched_sparse_v7;
+    separate_launches=True keeps one launch per projection (the default runs both in one cooperative
+    launch where the shapes allow it)."""
     dev = require_cuda(hidden_states, topk_weights, topk_ids, w13_comp, w13_meta, w13_scale, w13_g_scales,
                        w2_comp, w2_meta, w2_scale, w2_g_scales)
     _check_act(hidden_states, "hidden_states")
@@ -208,7 +211,8 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
             ptr(w13_comp), ptr(w13_meta), ptr(w13_scale), ptr(w13_g_scales), w13_scale.shape[1],
             ptr(w2_comp), ptr(w2_meta), ptr(w2_scale), ptr(w2_g_scales), w2_scale.shape[1],
             ptr(out), dtype_code(out.dtype), M, topk, H, I, E,
-            (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0) | _flags(meta_ordered, w13_meta, w2_meta),
+            (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0) | _flags(meta_ordered, w13_meta, w2_meta) |
+            (_lib.MOE_SEPARATE_LAUNCHES if separate_launches else 0),
             ptr(ws), ws.numel(), stream_ptr(dev)), "fused_sparse_moe_v7")
     return out
 
@@ -222,7 +226,7 @@ class FusedSparseMoE:
     per-call work to the three activation-side tensors.  Results are identical to the function's."""
 
     def __init__(self, w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales,
-                 inter_size: int, expert_map=None, meta_ordered=None):
+                 inter_size: int, expert_map=None, meta_ordered=None, separate_launches: bool = False):
         dev = require_cuda(w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales)
         for t, n in ((w13_comp, "w13_comp"), (w13_meta, "w13_meta"), (w13_scale, "w13_scale"), (w2_comp, "w2_comp"),
                      (w2_meta, "w2_meta"), (w2_scale, "w2_scale")):
@@ -244,7 +248,7 @@ class FusedSparseMoE:
             emap = (expert_map if expert_map.dtype == torch.int32 else expert_map.to(torch.int32)).contiguous()
         self.device = dev
         self._keep = (w13_comp, w13_meta, w13_scale, w13_g_scales, w2_comp, w2_meta, w2_scale, w2_g_scales, emap)
-        self._flags = _flags(meta_ordered, w13_meta, w2_meta)
+        self._flags = _flags(meta_ordered, w13_meta, w2_meta) | (_lib.MOE_SEPARATE_LAUNCHES if separate_launches else 0)
         self._head = (ptr(emap), 0 if emap is None else emap.numel(),
                       ptr(w13_comp), ptr(w13_meta), ptr(w13_scale), ptr(w13_g_scales), w13_scale.shape[1],
                       ptr(w2_comp), ptr(w2_meta), ptr(w2_scale), ptr(w2_g_scales), w2_scale.shape[1])
