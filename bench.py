@@ -12,8 +12,9 @@ combine over NCCL) and every GPU brings its own batch (weak scaling).
   value      device-timed whole-job tokens/s, inputs resident in HBM
   e2e        the same through the public op with host buffers (H2D of activations/routing and D2H
              of the result inside the timed region)
-  roofline   sparse GEMV kernel: algorithmic weight+activation bytes per launch / CUDA-event
-             duration of that launch, against the measured HBM copy bandwidth
+  roofline   sparse GEMV kernel (both projections of the layer, one cooperative launch): algorithmic
+             weight+activation bytes per launch / CUDA-event duration of that launch, against the
+             measured HBM copy bandwidth; per-projection times from separate launches alongside
   cpu_baseline  the reference's dequantize-to-bf16 emulation (oracle port, torch on the host cores)
 
 `--impl reference` times that CPU emulation as the main measurement instead.
