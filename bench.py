@@ -12,9 +12,9 @@ combine over NCCL) and every GPU brings its own batch (weak scaling).
   value      device-timed whole-job tokens/s, inputs resident in HBM
   e2e        the same through the public op with host buffers (H2D of activations/routing and D2H
              of the result inside the timed region)
-  roofline   sparse GEMV kernel (both projections of the layer, one cooperative launch): algorithmic
-             weight+activation bytes per launch / CUDA-event duration of that launch, against the
-             measured HBM copy bandwidth; per-projection times from separate launches alongside
+  roofline   sparse GEMV kernel (both projections of the layer): algorithmic weight+activation bytes /
+             CUDA-event duration of the two launches, against the measured HBM copy bandwidth;
+             per-projection times alongside
   cpu_baseline  the reference's dequantize-to-bf16 emulation (oracle port, torch on the host cores)
 
 `--impl reference` times that CPU emulation as the main measurement instead.
@@ -565,7 +565,8 @@ def main():
             uniq.append(int(m[m >= 0].unique().numel()))
         L.b200fp4_fused_moe_profile_events(0, 0, 0)
     torch.cuda.synchronize()
-    # the layer's default path runs both projections in one cooperative launch: events 0 -> 2 bracket it
+    # events 0 -> 2 bracket the two projections of the layer's default path (two launches at this batch
+    # size; one cooperative launch up to 256 pairs)
     t_both = [evs[i][0].elapsed_time(evs[i][2]) * 1e-3 for i in range(args.steps)]
     # per-projection times: the same layer with one launch per projection (a few steps, cold L2)
     k4 = ("comp_T", "meta_T", "scale_T", "g_scales")
@@ -594,8 +595,8 @@ def main():
     traffic = (233.61e6 + 118.83e6) / 244.0 * statistics.mean(uniq)
     roofline = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
                 "traffic": traffic, "peak_kind": f"{peak_kind} copy bandwidth",
-                "kernel": "fused_moe_mma_kernel: sparse_gemv_mma gate_up+SiLU and down projections of one layer in one cooperative launch",
-                "per_launch_us": {"both_projections_one_launch": statistics.mean(t_both) * 1e6,
+                "kernel": "sparse_gemv_mma_kernel: gate_up+SiLU and down projections of one layer (tensor-core 2:4 GEMV)",
+                "per_launch_us": {"both_projections": statistics.mean(t_both) * 1e6,
                                   "gate_up_separate_launch": statistics.mean(t_gu) * 1e6,
                                   "down_separate_launch": statistics.mean(t_dn) * 1e6},
                 "algorithmic_bytes_per_step": (sum(b_gu) + sum(b_dn)) / args.steps,

@@ -52,7 +52,7 @@ struct Plan {
   int* hdr;        // [0] = number of unique experts, [1] = number of passes
   int* pairs;      // [P]  pair indices grouped by expert
   int* mapped;     // [P]  local expert id of each pair, or -1
-  int4* pass_rec;  // [passes][2]: {expert, n_tokens, pair0, pair1}, {pair2, pair3, -, -}
+  int4* pass_rec;  // [passes][2]: {expert, n_tokens, pair0, pair1}, {pair2, pair3, index of pair0 in pairs[], -}
 };
 
 struct GemvArgs {
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
                     Plan plan, const __nv_bfloat16* __restrict__ conv_src, __half* __restrict__ conv_dst,
                     int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks,
-                    int* zero_buf, int zero_count) {
+                    int* zero_buf, int zero_count, int max_tok) {
   if (blockIdx.x > 0) {
     const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
     for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kPlanThreads)
       const int c = s_count[e];
       sum[0] += c;
       sum[1] += c > 0;
-      sum[2] += (c + kMaxTok - 1) / kMaxTok;
+      sum[2] += (c + max_tok - 1) / max_tok;
     }
   }
   int inc[3] = {sum[0], sum[1], sum[2]};
@@ -178,13 +178,14 @@ __global__ void __launch_bounds__(kPlanThreads)
       const int e = e0 + i;
       if (e < E) {
         const int end = s_count[e];
-        for (int s0 = start; s0 < end; s0 += kMaxTok) {
-          const int nt = min(kMaxTok, end - s0);
+        for (int s0 = start; s0 < end; s0 += max_tok) {
+          const int nt = min(max_tok, end - s0);
           int pr[4];
 #pragma unroll
           for (int t = 0; t < 4; ++t) pr[t] = t < nt ? plan.pairs[s0 + t] : 0;
+          // pairs 4.. of an 8-token pass are read from pairs[] (the run of an expert is contiguous there)
           plan.pass_rec[2 * pass] = make_int4(e, nt, pr[0], pr[1]);
-          plan.pass_rec[2 * pass + 1] = make_int4(pr[2], pr[3], 0, 0);
+          plan.pass_rec[2 * pass + 1] = make_int4(pr[2], pr[3], s0, 0);
           ++pass;
         }
         start = end;
@@ -541,6 +542,38 @@ __global__ void zero_unmapped_rows_kernel(const int* __restrict__ mapped, int P,
   for (int n = threadIdx.x; n < N; n += blockDim.x) store_out(out, out_dtype, (int64_t)p * ldo + n, 0.f);
 }
 
+// Pass record of the tensor-core kernel: up to TM (4 or 8) pairs.
+template <int TM>
+struct RecT {
+  int e, nt;
+  int p[TM];
+  __device__ __forceinline__ int pair(int t) const {
+    int v = p[0];
+#pragma unroll
+    for (int i = 1; i < TM; ++i) v = (t == i) ? p[i] : v;
+    return v;
+  }
+};
+template <int TM>
+__device__ __forceinline__ RecT<TM> load_rec_t(const Plan& plan, int pass) {
+  const int4 x = plan.pass_rec[2 * pass], y = plan.pass_rec[2 * pass + 1];
+  RecT<TM> r;
+  r.e = x.x; r.nt = x.y; r.p[0] = x.z; r.p[1] = x.w; r.p[2] = y.x; r.p[3] = y.y;
+  if (TM == 8) {
+#pragma unroll
+    for (int i = 4; i < TM; ++i) r.p[i] = (i < r.nt) ? plan.pairs[y.z + i] : 0;
+  }
+  return r;
+}
+template <int TM>
+__device__ __forceinline__ RecT<TM> empty_rec_t() {
+  RecT<TM> r;
+  r.e = -1; r.nt = 0;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) r.p[i] = 0;
+  return r;
+}
+
 // ------------------------------------------------------------------------------------------ tensor-core GEMV
 //
 // Same work items as sparse_gemv_kernel, but the 2:4 gather and the multiply-accumulate run on the
@@ -635,8 +668,11 @@ __device__ __forceinline__ __half2 e4m3x2_to_h2(uint32_t w) {
 // they run in one launch: 1 = producer (done[pass] is incremented once an item's output is stored and
 // fenced), 2 = consumer (the activations of a pass are staged only after done[pass] has reached
 // `need` = producer slabs per pass), 0 = stand-alone.
-template <int CG, int S, bool kSilu, int kDep>
+// TM = tokens per pass (4 or 8; the instruction's B operand has 8 columns either way, but the
+// activation buffers and the partial-sum scratch double with 8).
+template <int CG, int S, bool kSilu, int kDep, int TM>
 __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char* smem, int* done, int need) {
+  using Rec = RecT<TM>;
   constexpr int KSL = kMmaWarps / CG;          // K-slices per item
   constexpr int VCOLS = 128 * CG;              // columns of a slab (SiLU: 64*CG gate + 64*CG up)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -647,12 +683,13 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
   const int grid = gridDim.x;
 
   // ---- shared memory map (shared-window addresses)
-  //   activations of the current and the next pass [2][4][K + 8] fp16 | partial sums | 16 rings of S stages
+  //   activations of the current and the next pass [2][TM][K + 8] fp16 | partial sums (one block of
+  //   kMmaRedBytes per four tokens) | 16 rings of S stages
   const uint32_t a_pitch = 2u * (uint32_t)K + 16u;
   const uint32_t sa = (shared_addr(smem) + 1023u) & ~1023u;
-  const uint32_t red = sa + ((8u * a_pitch + 1023u) & ~1023u);
+  const uint32_t red = sa + ((2u * TM * a_pitch + 1023u) & ~1023u);
   const uint32_t ring_bytes = S * kMmaStageBytes;
-  const uint32_t ring = red + kMmaRedBytes + (uint32_t)warp * ring_bytes;
+  const uint32_t ring = red + (TM / 4) * kMmaRedBytes + (uint32_t)warp * ring_bytes;
   const uint32_t ring_end = ring + ring_bytes;
 
   // ---- items of this block: blockIdx.x, + grid, ...
@@ -661,19 +698,19 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
   const int my_items = (int)blockIdx.x < n_items ? (n_items - 1 - (int)blockIdx.x) / grid + 1 : 0;
   if (my_items == 0) return;
   auto pass_of = [&](int i) { return ((int)blockIdx.x + i * grid) / n_slabs; };
-  Rec rc = load_rec(g.plan.pass_rec, pass_of(0));
-  Rec rn = my_items > 1 ? load_rec(g.plan.pass_rec, pass_of(1)) : empty_rec();
+  Rec rc = load_rec_t<TM>(g.plan, pass_of(0));
+  Rec rn = my_items > 1 ? load_rec_t<TM>(g.plan, pass_of(1)) : empty_rec_t<TM>();
   int e_nn = my_items > 2 ? g.plan.pass_rec[2 * pass_of(2)].x : -1;
 
   const int chunks = K >> 3;
   auto issue_A = [&](const Rec& r, int buf) {
 #pragma unroll
-    for (int tk = 0; tk < 4; ++tk)
+    for (int tk = 0; tk < TM; ++tk)
       if (tk < r.nt) {
-        const uint32_t pr = (uint32_t)r.pair(tk);
+        const uint32_t pr = (uint32_t)r.p[tk];
         const int64_t row = g.a_magic ? (int64_t)__umulhi(pr, g.a_magic) : (int64_t)pr;
         const __half* src = g.A + row * g.lda;
-        const uint32_t dst = sa + (uint32_t)(buf * 4 + tk) * a_pitch;
+        const uint32_t dst = sa + (uint32_t)(buf * TM + tk) * a_pitch;
         for (int ch = tid; ch < chunks; ch += kMmaThreads) cp_async16_s(dst + (uint32_t)ch * 16u, src + ch * 8);
       }
   };
@@ -762,18 +799,20 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
   const uint32_t off_comp = (uint32_t)t * 128u + (uint32_t)q * 16u;
   const uint32_t off_meta = 1024u + (uint32_t)(2 * (t & 1)) * 128u + (uint32_t)q * 16u + (uint32_t)(t >> 1) * 8u;
   const uint32_t off_scale = 1536u + (uint32_t)q * 16u;
-  // B column q = token q & 3 (columns 4..7 repeat the four tokens; their results are never read), k = 32*ks + 2t (+8i)
-  const uint32_t off_b = (uint32_t)(q & 3) * a_pitch + (uint32_t)t * 4u + (uint32_t)ks * 64u;
+  // B column q = token q (with four tokens per pass columns 4..7 repeat them; their results are never read),
+  // k = 32*ks + 2t (+8i)
+  const uint32_t off_b = (uint32_t)(TM == 8 ? q : (q & 3)) * a_pitch + (uint32_t)t * 4u + (uint32_t)ks * 64u;
   // scratch [warp][column 0..127][token 0..3]; the 16-byte token groups of a column are XOR-swizzled
   // by the column's quad so that neither side has bank conflicts
-  const uint32_t red_w = red + (uint32_t)warp * 2048u + (uint32_t)q * 256u + 8u * (uint32_t)(t & 1) +
-                         16u * (uint32_t)((q ^ ((cgw & 1) << 2)) & 7);
+  // (tokens 4..7 of an 8-token pass, held by lanes t = 2, 3, go to a second block of the same shape)
+  const uint32_t red_w = red + (uint32_t)(t >> 1) * kMmaRedBytes + (uint32_t)warp * 2048u + (uint32_t)q * 256u +
+                         8u * (uint32_t)(t & 1) + 16u * (uint32_t)((q ^ ((cgw & 1) << 2)) & 7);
 
   uint32_t c_st = ring;
   int abuf = 0;
   for (; i_cur < my_items; ++i_cur) {
     const int slab = ((int)blockIdx.x + i_cur * grid) % n_slabs;
-    Rec rnn = i_cur + 2 < my_items ? load_rec(g.plan.pass_rec, pass_of(i_cur + 2)) : empty_rec();
+    Rec rnn = i_cur + 2 < my_items ? load_rec_t<TM>(g.plan, pass_of(i_cur + 2)) : empty_rec_t<TM>();
     const int e_n3 = i_cur + 3 < my_items ? g.plan.pass_rec[2 * pass_of(i_cur + 3)].x : -1;
     const float gmul = g.w.g[rc.e];
     // the group that carried this pass's activations is followed by nstep - 1 newer ones
@@ -791,7 +830,7 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
-    uint32_t ab = sa + (uint32_t)abuf * 4u * a_pitch + off_b;
+    uint32_t ab = sa + (uint32_t)abuf * TM * a_pitch + off_b;
 
     for (int js = 0; js < nstep; ++js) {
       cp_async_wait<S - 2>();
@@ -849,8 +888,8 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
     // K-slice s and column group cw is s * CG + cw.
     auto slice_sum = [&](int v, int tok) {
       const int cw = v >> 7, col = v & 127;
-      const uint32_t a = red + (uint32_t)cw * 2048u + (((uint32_t)col * 16u) ^ ((uint32_t)(((col >> 4) ^ ((cw & 1) << 2)) & 7) << 4)) +
-                         (uint32_t)tok * 4u;
+      const uint32_t a = red + (uint32_t)(tok >> 2) * kMmaRedBytes + (uint32_t)cw * 2048u +
+                         (((uint32_t)col * 16u) ^ ((uint32_t)(((col >> 4) ^ ((cw & 1) << 2)) & 7) << 4)) + (uint32_t)(tok & 3) * 4u;
       float sum = 0.f;
 #pragma unroll
       for (int s = 0; s < KSL; ++s) sum += __uint_as_float(lds32_at(a + (uint32_t)(s * CG) * 2048u));
@@ -858,9 +897,9 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
     };
     if (kSilu) {
 #pragma unroll
-      for (int r = 0; r < CG; ++r) {
-        const int idx = r * 256 + warp * 16 + (lane & 15);
-        const int col_g = idx >> 2, tok = idx & 3;
+      for (int r = 0; r < CG * (TM / 4); ++r) {
+        const int idx = (r % CG) * 256 + warp * 16 + (lane & 15);
+        const int col_g = idx >> 2, tok = (idx & 3) + 4 * (r / CG);
         const float sum = slice_sum(col_g + (lane >> 4) * (64 * CG), tok);
         const float other = __shfl_down_sync(0xffffffffu, sum, 16);
         if (lane < 16 && tok < rc.nt) {
@@ -871,9 +910,9 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
       }
     } else {
 #pragma unroll
-      for (int r = 0; r < CG; ++r) {
-        const int x = r * 512 + tid;
-        const int v = x >> 2, tok = x & 3;
+      for (int r = 0; r < CG * (TM / 4); ++r) {
+        const int x = (r % CG) * 512 + tid;
+        const int v = x >> 2, tok = (x & 3) + 4 * (r / CG);
         const float sum = slice_sum(v, tok);
         if (tok < rc.nt) store_out(g.out, g.out_dtype, (int64_t)rc.pair(tok) * g.ldo + slab * VCOLS + v, sum * gmul);
       }
@@ -891,10 +930,10 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
   }
 }
 
-template <int CG, int S, bool kSilu>
+template <int CG, int S, bool kSilu, int TM>
 __global__ void __launch_bounds__(kMmaThreads, 1) sparse_gemv_mma_kernel(const GemvArgs g) {
   extern __shared__ __align__(16) unsigned char smem[];
-  gemv_mma_phase<CG, S, kSilu, 0>(g, smem, nullptr, 0);
+  gemv_mma_phase<CG, S, kSilu, 0, TM>(g, smem, nullptr, 0);
 }
 
 // Both projections of the MoE layer in one launch: every block first walks its gate_up items, then its
@@ -902,13 +941,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1) sparse_gemv_mma_kernel(const G
 // gate_up items start on the down projection of passes finished long ago instead of idling through
 // the last, partial round and a second kernel's ramp-up.  Launched cooperatively (all blocks
 // co-resident), so a block polling for a pass can never keep the block that produces it off the GPU.
-template <int CGA, int SA, int CGB, int SB>
+template <int CGA, int SA, int CGB, int SB, int TM>
 __global__ void __launch_bounds__(kMmaThreads, 1)
     fused_moe_mma_kernel(const GemvArgs ga, const GemvArgs gb, int* done, int need) {
   extern __shared__ __align__(16) unsigned char smem[];
-  gemv_mma_phase<CGA, SA, true, 1>(ga, smem, done, need);
+  gemv_mma_phase<CGA, SA, true, 1, TM>(ga, smem, done, need);
   __syncthreads();              // the second phase lays shared memory out anew
-  gemv_mma_phase<CGB, SB, false, 2>(gb, smem, done, need);
+  gemv_mma_phase<CGB, SB, false, 2, TM>(gb, smem, done, need);
 }
 
 // ------------------------------------------------------------------------------------------ generic
@@ -1059,20 +1098,20 @@ int launch_gemv_t(const GemvArgs& g, int64_t grid, size_t smem, cudaStream_t st)
 
 // ---- tensor-core kernel: configuration and launch
 struct MmaCfg {
-  int cg, stages;
+  int cg, stages, tm;
   bool ok;
 };
 
-size_t mma_smem_bytes(int64_t K, int stages) {
-  const size_t a_bytes = align_up((size_t)8 * (2 * (size_t)K + 16), 1024);
-  return 1024 + a_bytes + kMmaRedBytes + (size_t)kMmaWarps * stages * kMmaStageBytes;
+size_t mma_smem_bytes(int64_t K, int stages, int tm) {
+  const size_t a_bytes = align_up((size_t)2 * tm * (2 * (size_t)K + 16), 1024);
+  return 1024 + a_bytes + (size_t)(tm / 4) * kMmaRedBytes + (size_t)kMmaWarps * stages * kMmaStageBytes;
 }
 
 // `passes` is an upper bound of the number of passes (the real number is only known on the device).
 // Wide items (more column groups) have less per-item work to amortise, but with few passes they leave
 // SMs without an item, so small batches take the narrowest shape that is allowed.
-MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu, int64_t passes) {
-  MmaCfg c = {0, 0, false};
+MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu, int64_t passes, int tm) {
+  MmaCfg c = {0, 0, tm, false};
   if (G != K / 16 || K % 32 != 0) return c;
   const int order_silu[3] = {2, 4, 1}, order_plain[3] = {4, 2, 1};
   const int order_small[3] = {1, 2, 4};
@@ -1084,7 +1123,7 @@ MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu, int64_t pas
     const bool cols_ok = inter_silu > 0 ? (inter_silu % (64 * cg) == 0 && N == 2 * (int64_t)inter_silu) : (N % (128 * cg) == 0);
     if (cols_ok && K % (32 * ksl) == 0 && K / (32 * ksl) >= 2) {
       for (int s = 5; s >= 3; s -= 2)
-        if (mma_smem_bytes(K, s) <= 227 * 1024 && (s - 2 < 2 * (int)(K / (32 * ksl)))) {
+        if (mma_smem_bytes(K, s, tm) <= 227 * 1024 && (s - 2 < 2 * (int)(K / (32 * ksl)))) {
           c.cg = cg;
           c.stages = s;
           c.ok = true;
@@ -1095,33 +1134,43 @@ MmaCfg pick_mma_cfg(int64_t N, int64_t K, int64_t G, int inter_silu, int64_t pas
   return c;
 }
 
-template <int CG, int S, bool kSilu>
+template <int CG, int S, bool kSilu, int TM>
 int launch_mma_t(const GemvArgs& g, int64_t grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(sparse_gemv_mma_kernel<CG, S, kSilu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(sparse_gemv_mma_kernel<CG, S, kSilu, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              227 * 1024) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
     attr_set[dev] = true;
   }
-  sparse_gemv_mma_kernel<CG, S, kSilu><<<(unsigned)grid, kMmaThreads, mma_smem_bytes(g.K, S), st>>>(g);
+  sparse_gemv_mma_kernel<CG, S, kSilu, TM><<<(unsigned)grid, kMmaThreads, mma_smem_bytes(g.K, S, TM), st>>>(g);
   return B200FP4_STATUS_SUCCESS;
 }
 
 template <bool kSilu>
 int launch_mma(const GemvArgs& g, const MmaCfg& c, int64_t grid, cudaStream_t st) {
-  if (c.stages == 5) {
-    if (c.cg == 1) return launch_mma_t<1, 5, kSilu>(g, grid, st);
-    if (c.cg == 2) return launch_mma_t<2, 5, kSilu>(g, grid, st);
-    return launch_mma_t<4, 5, kSilu>(g, grid, st);
+  if (c.tm == 8) {
+    if (c.stages == 5) {
+      if (c.cg == 1) return launch_mma_t<1, 5, kSilu, 8>(g, grid, st);
+      if (c.cg == 2) return launch_mma_t<2, 5, kSilu, 8>(g, grid, st);
+      return launch_mma_t<4, 5, kSilu, 8>(g, grid, st);
+    }
+    if (c.cg == 1) return launch_mma_t<1, 3, kSilu, 8>(g, grid, st);
+    if (c.cg == 2) return launch_mma_t<2, 3, kSilu, 8>(g, grid, st);
+    return launch_mma_t<4, 3, kSilu, 8>(g, grid, st);
   }
-  if (c.cg == 1) return launch_mma_t<1, 3, kSilu>(g, grid, st);
-  if (c.cg == 2) return launch_mma_t<2, 3, kSilu>(g, grid, st);
-  return launch_mma_t<4, 3, kSilu>(g, grid, st);
+  if (c.stages == 5) {
+    if (c.cg == 1) return launch_mma_t<1, 5, kSilu, 4>(g, grid, st);
+    if (c.cg == 2) return launch_mma_t<2, 5, kSilu, 4>(g, grid, st);
+    return launch_mma_t<4, 5, kSilu, 4>(g, grid, st);
+  }
+  if (c.cg == 1) return launch_mma_t<1, 3, kSilu, 4>(g, grid, st);
+  if (c.cg == 2) return launch_mma_t<2, 3, kSilu, 4>(g, grid, st);
+  return launch_mma_t<4, 3, kSilu, 4>(g, grid, st);
 }
 
 template <bool kScale8, bool kSilu>
@@ -1162,7 +1211,8 @@ int check_common(const void* A, int a_dtype, const void* out, int out_dtype, int
 // Plan + (for bf16 activations) conversion to fp16 in one launch.
 void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld, const int32_t* expert_map,
                  int64_t global_E, int64_t E, const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_rows,
-                 int64_t a_cols, int64_t a_ld, cudaStream_t st, int* zero_buf = nullptr, int zero_count = 0) {
+                 int64_t a_cols, int64_t a_ld, cudaStream_t st, int* zero_buf = nullptr, int zero_count = 0,
+                 int max_tok = kMaxTok) {
   int64_t chunks = 0;
   unsigned blocks = 1;
   if (a_bf16 != nullptr) {
@@ -1174,7 +1224,7 @@ void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld
   moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan,
                                                    reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks,
                                                    (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8, zero_buf,
-                                                   zero_count);
+                                                   zero_count, max_tok);
 }
 
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
@@ -1200,10 +1250,11 @@ GemvArgs make_args(const SparseWeights& w, const Plan& plan, const __half* A, in
 // Both projections of the layer in one cooperative launch (tensor-core kernel).  Returns
 // NOT_SUPPORTED when the shapes do not map to one of the instantiated pairs of configurations or the
 // device cannot keep all blocks resident; the caller then launches the projections one by one.
-template <int CGA, int CGB>
+template <int CGA, int SA, int CGB, int SB, int TM>
 int launch_fused_pair(GemvArgs ga, GemvArgs gb, int* done, int64_t P, int64_t E, cudaStream_t st) {
-  const void* fn = reinterpret_cast<const void*>(&fused_moe_mma_kernel<CGA, 5, CGB, 5>);
-  const size_t smem = mma_smem_bytes(ga.K, 5) > mma_smem_bytes(gb.K, 5) ? mma_smem_bytes(ga.K, 5) : mma_smem_bytes(gb.K, 5);
+  const void* fn = reinterpret_cast<const void*>(&fused_moe_mma_kernel<CGA, SA, CGB, SB, TM>);
+  const size_t sa = mma_smem_bytes(ga.K, SA, TM), sb = mma_smem_bytes(gb.K, SB, TM);
+  const size_t smem = sa > sb ? sa : sb;
   static int state[64] = {0};     // per device: 0 unknown, 1 usable, -1 not usable
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1234,12 +1285,12 @@ int launch_fused_pair(GemvArgs ga, GemvArgs gb, int* done, int64_t P, int64_t E,
 
 int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
                    int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t G, int64_t E, int inter_silu,
-                   bool meta_ordered, cudaStream_t st) {
+                   bool meta_ordered, cudaStream_t st, int tm = kMaxTok) {
   GemvArgs g = make_args(w, plan, A, lda, a_div, out, out_dtype, ldo, N, K, inter_silu);
   const bool s8 = (G == K / 8);
   if (meta_ordered) {
     // tensor-core kernel where the shape allows it (one scale per 16 k, whole 128-column groups)
-    const MmaCfg mc = pick_mma_cfg(N, K, G, inter_silu, P < E ? P : E);
+    const MmaCfg mc = pick_mma_cfg(N, K, G, inter_silu, P < E ? P : E, tm);
     if (mc.ok) {
       g.n_slabs = inter_silu > 0 ? inter_silu / (64 * mc.cg) : (int)(N / (128 * mc.cg));
       int64_t grid = max_passes(P, E) * g.n_slabs;
@@ -1248,6 +1299,7 @@ int run_projection(const SparseWeights& w, const Plan& plan, const __half* A, in
       return inter_silu > 0 ? launch_mma<true>(g, mc, grid, st) : launch_mma<false>(g, mc, grid, st);
     }
   }
+  if (tm != kMaxTok) return B200FP4_STATUS_NOT_SUPPORTED;   // the general kernel only knows four-token passes
   const GemvCfg c = pick_cfg(K, s8);
   if (!c.ok) return B200FP4_STATUS_NOT_SUPPORTED;
   const int slab = c.cg * c.cols;
@@ -1480,20 +1532,36 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   int* done = reinterpret_cast<int*>(ws + off);
   const int64_t n_done = max_passes(P, E);
 
+  // Tokens per pass: eight when the local experts see four or more tokens each on average (large
+  // batches, expert parallelism with many source ranks) and both projections have a tensor-core
+  // configuration for it; four otherwise.
+  const int64_t pb = P < E ? P : E;
+  const int64_t local_pairs = (expert_map && global_E > 0) ? P * E / global_E : P;
+  int tm = kMaxTok;
+  if (ordered && local_pairs >= 4 * E) {
+    const MmaCfg a8 = pick_mma_cfg(2 * I, H, G13, (int)I, pb, 8), b8 = pick_mma_cfg(H, I, G2, 0, pb, 8);
+    if (a8.ok && b8.ok) tm = 8;
+  }
   launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, bf ? hidden : nullptr, h16, M, H, ld_h, st, done,
-              (int)n_done);
+              (int)n_done, tm);
   if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
-  if (ordered && !(flags & B200FP4_MOE_SEPARATE_LAUNCHES)) {
-    // one cooperative launch for both projections when both take the tensor-core kernel with five ring stages
-    const int64_t pb = P < E ? P : E;
-    const MmaCfg ca = pick_mma_cfg(2 * I, H, G13, (int)I, pb), cb = pick_mma_cfg(H, I, G2, 0, pb);
-    if (ca.ok && cb.ok && ca.stages == 5 && cb.stages == 5) {
+  // One cooperative launch for both projections pays for small batches (measured on B200: 24.6 vs 27.2 us
+  // per layer at 10 pairs, 67.7 vs 68.2 us at 160); from 320 pairs on two launches are faster (100.6 vs
+  // 102.3 us, 185.6 vs 193.8 us at 1280 pairs), so it is used up to 256 pairs.
+  if (ordered && !(flags & B200FP4_MOE_SEPARATE_LAUNCHES) && P <= 256) {
+    const MmaCfg ca = pick_mma_cfg(2 * I, H, G13, (int)I, pb, tm), cb = pick_mma_cfg(H, I, G2, 0, pb, tm);
+    if (ca.ok && cb.ok) {
       const GemvArgs ga = make_args(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk,
                                     act, B200FP4_DTYPE_F16, I, 2 * I, H, (int)I);
       const GemvArgs gb = make_args(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, H, I, 0);
       int frc = B200FP4_STATUS_NOT_SUPPORTED;
-      if (ca.cg == 2 && cb.cg == 4) frc = launch_fused_pair<2, 4>(ga, gb, done, P, E, st);
-      else if (ca.cg == 1 && cb.cg == 2) frc = launch_fused_pair<1, 2>(ga, gb, done, P, E, st);
+      if (tm == 4 && ca.stages == 5 && cb.stages == 5) {
+        if (ca.cg == 2 && cb.cg == 4) frc = launch_fused_pair<2, 5, 4, 5, 4>(ga, gb, done, P, E, st);
+        else if (ca.cg == 1 && cb.cg == 2) frc = launch_fused_pair<1, 5, 2, 5, 4>(ga, gb, done, P, E, st);
+      } else if (tm == 8 && ca.stages == 3 && cb.stages == 5) {
+        if (ca.cg == 2 && cb.cg == 4) frc = launch_fused_pair<2, 3, 4, 5, 8>(ga, gb, done, P, E, st);
+        else if (ca.cg == 1 && cb.cg == 2) frc = launch_fused_pair<1, 3, 2, 5, 8>(ga, gb, done, P, E, st);
+      }
       if (frc == B200FP4_STATUS_SUCCESS) {
         if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
         if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
@@ -1505,10 +1573,10 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
     }
   }
   rc = run_projection(w13, plan, bf ? h16 : reinterpret_cast<const __half*>(hidden), bf ? H : ld_h, (int)topk, act,
-                      B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, ordered, st);
+                      B200FP4_DTYPE_F16, I, P, 2 * I, H, G13, E, (int)I, ordered, st, tm);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
-  rc = run_projection(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, ordered, st);
+  rc = run_projection(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, G2, E, 0, ordered, st, tm);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);

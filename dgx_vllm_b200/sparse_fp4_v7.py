@@ -169,8 +169,8 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
     hidden_states [M,H] f16/bf16; topk_weights [M,topk] f32; topk_ids [M,topk] int; expert_map [global_E]
     int32 or an empty tensor / None for identity; w13_* [E,H/4,2I], [E,H/8,2I], [E,G,2I], [E];
     w2_* [E,I/4,H], [E,I/8,H], [E,G,H], [E].  Returns [M,H].  meta_ordered as in batched_sparse_v7;
-    separate_launches=True keeps one launch per projection (the default runs both in one cooperative
-    launch where the shapes allow it)."""
+    separate_launches=True keeps one launch per projection (by default small batches, up to 256
+    (token, expert) pairs, run both in one cooperative launch where the shapes allow it)."""
     dev = require_cuda(hidden_states, topk_weights, topk_ids, w13_comp, w13_meta, w13_scale, w13_g_scales,
                        w2_comp, w2_meta, w2_scale, w2_g_scales)
     _check_act(hidden_states, "hidden_states")

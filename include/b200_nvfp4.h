@@ -216,10 +216,10 @@ B200FP4_API int b200fp4_convert_to_sparse_2of4(const uint8_t* codes, const uint8
  *   workspace   b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E) bytes
  * flags: B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT (the reference's apply_router_weight_on_input) sums the
  * expert outputs unweighted, exactly as the reference kernel does (sparse_fp4_v7.cu:592-594);
- * B200FP4_SPARSE_META_ORDERED as described above, for both weight sets.  With ordered metadata and
- * the usual shapes both projections run in ONE cooperative launch (blocks that finish their share
- * of gate_up move on to the down projection of passes that are already complete);
- * B200FP4_MOE_SEPARATE_LAUNCHES keeps one launch per projection (e.g. to time them separately). */
+ * B200FP4_SPARSE_META_ORDERED as described above, for both weight sets.  With ordered metadata, the
+ * usual shapes and up to 256 (token, expert) pairs both projections run in ONE cooperative launch
+ * (blocks that finish their share of gate_up move on to the down projection of passes that are
+ * already complete); B200FP4_MOE_SEPARATE_LAUNCHES keeps one launch per projection. */
 B200FP4_API size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I,
                                                      int64_t E);
 B200FP4_API int b200fp4_fused_sparse_moe(

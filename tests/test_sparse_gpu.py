@@ -310,3 +310,20 @@ def test_bound_layer_object_matches_function():
         assert torch.equal(out, ref)
     with pytest.raises(RuntimeError):
         layer(hidden.cuda()[:, :512].contiguous(), tw.cuda(), ids.cuda())
+
+
+@pytest.mark.parametrize("M,topk,E,H,I,separate", [
+    (64, 8, 16, 2048, 512, False),      # 32 tokens per expert on average: eight-token passes, one launch
+    (64, 8, 16, 2048, 512, True),       # ... and one launch per projection
+    (48, 6, 8, 1024, 256, False),       # shapes that take other slab widths
+])
+def test_fused_moe_eight_token_passes(M, topk, E, H, I, separate):
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    w13, w2, tw, ids, hidden = _moe_case(E, H, I, M, topk, seed=M + E + I)
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    out = sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), None, *c(w13), *c(w2), I, False,
+                                  separate_launches=separate)
+    ref = _ref_fused(w13, w2, tw, ids, hidden, I)
+    assert rel_err(to_np(out), ref) < TOL
+    general = sp7.fused_sparse_moe_v7(hidden.cuda(), tw.cuda(), ids.cuda(), None, *c(w13), *c(w2), I, False, meta_ordered=False)
+    assert rel_err(to_np(general), ref) < TOL
