@@ -2,9 +2,11 @@
 //
 // Replaces sparse_fp4_kernel/sparse_fp4_v7.cu of the reference with a different execution plan:
 //   * a "plan" kernel groups the (token, expert) pairs by expert and cuts them into passes of at
-//     most four tokens, so an expert's weights are streamed from HBM once per layer (per pass)
-//     instead of once per pair;
-//   * a persistent GEMV kernel (one block per SM) walks (pass, column slab) work items.  A thread
+//     most four (or eight) tokens, so an expert's weights are streamed from HBM once per layer (per
+//     pass) instead of once per pair;
+//   * two persistent GEMV kernels (one block per SM) walk (pass, column slab) work items: the
+//     tensor-core kernel further down (mma.sp; needs ordered metadata indices and one scale per 16 k)
+//     and the general kernel described here, which takes any metadata.  In the general kernel a thread
 //     owns 16 output columns and one K-slice.  Its weight bytes (four compressed rows, two
 //     metadata rows, one scale row per 16 k) arrive through a private multi-stage cp.async ring in
 //     shared memory that keeps running across work-item boundaries, so HBM latency is hidden
@@ -579,7 +581,7 @@ __device__ __forceinline__ RecT<TM> empty_rec_t() {
 // Same work items as sparse_gemv_kernel, but the 2:4 gather and the multiply-accumulate run on the
 // tensor cores: the weights are the sparse A operand of mma.sp m16n8k32 (f16, fp32 accumulate), the
 // reference's metadata bytes are -- after one byte permute -- the instruction's metadata operand, and
-// the (up to four) tokens of the pass are columns of B.  What is left for the CUDA cores is the
+// the (up to four, or eight) tokens of the pass are columns of B.  What is left for the CUDA cores is the
 // E2M1 -> half2 decode (cvt.rn.f16x2.e2m1x2 straight from a byte of the loaded word), the E4M3 ->
 // half2 decode of the block scales (cvt.rn.f16x2.e4m3x2) and one half2 multiply per pair of weights
 // (E2M1 x E4M3 is exact in fp16).
