@@ -304,7 +304,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int col0 = ti.n0 + c * 32;
           if (col0 < p.N) {
             uint16_t* dst = dst_row + col0;
-            if (col0 + 32 <= p.N && (p.N % 8) == 0) {
+            if (col0 + 32 <= p.N && (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+              // 32-byte stores: whole sectors, half as many store instructions as 16-byte ones
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                st_global_v8(dst + 16 * i, &packed[c * 16 + 8 * i]);
+            } else if (col0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
               for (int i = 0; i < 4; ++i)
                 reinterpret_cast<uint4*>(dst)[i] = make_uint4(packed[c * 16 + 4 * i], packed[c * 16 + 4 * i + 1],
