@@ -36,7 +36,7 @@ int launch_gemm_tall(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kGemmThreads = 320;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 scale factors
+constexpr int kGemmThreads = 448;         // warp 0 TMA, warp 1 MMA, warps 2-5 and 10-13 epilogue, warps 6-9 scale factors
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < C::kAcc; ++a) {
       mbar_init(smem_u32(&acc_full[a]), 1);
-      mbar_init(smem_u32(&acc_empty[a]), 4);      // one arrival per epilogue warp
+      mbar_init(smem_u32(&acc_empty[a]), 8);      // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (ok) tcgen05_commit(smem_u32(&acc_full[acc]));
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < 10) {
     // ------------------------------------------------------------------ scale factors (warps 6..9)
     // Each warp owns one 32-lane quarter of tensor memory.  Lane L needs row L of every 32x16-byte
     // scale tile (the four quarters hold identical copies), so each lane moves 16 bytes from shared
@@ -254,10 +254,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    // (Two warps per lane quarter, each draining half of the columns, measured the same on B200:
-    // 154.7 vs 153 us at M=4096, N=14336, K=4096.)
+    // ------------------------------------------------------------------ epilogue (warps 2..5 and 10..13)
+    // Two warps per tensor-memory lane quarter, each draining and storing half of the tile's columns.
+    // With long K the epilogue hides behind the next tile either way; with short K (the grouped down
+    // projection: 8 MMAs per tile) the kernel is bound by how fast a tile can be drained and stored.
     const int quarter = warp & 3;                 // tensor-memory lanes [32*quarter, +32) belong to this warp
+    constexpr int CH = BN / 64;                   // 32-column chunks per warp
+    const int c_first = warp >= 10 ? CH : 0;
     const float alpha_dense = kGrouped ? 0.f : p.alpha[0];
     uint32_t tcount = 0;
     bool ok = true;
@@ -272,11 +275,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int row = ti.a_row0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       // drain this thread's row of the accumulator into packed 16-bit registers ...
-      uint32_t packed[BN / 2];
+      uint32_t packed[BN / 4];
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < CH; ++c) {
         uint32_t r[32];
-        tcgen05_ld_32x32(taddr + c * 32, r);
+        tcgen05_ld_32x32(taddr + (c_first + c) * 32, r);
         tcgen05_wait_ld();
         if (p.out_bf16) {
 #pragma unroll
@@ -300,8 +303,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (row < ti.row_end) {
         uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = ti.n0 + c * 32;
+        for (int c = 0; c < CH; ++c) {
+          const int col0 = ti.n0 + (c_first + c) * 32;
           if (col0 < p.N) {
             uint16_t* dst = dst_row + col0;
             if (col0 + 32 <= p.N && (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
