@@ -95,11 +95,37 @@ __global__ void __launch_bounds__(kTX* kTY)
   // With one global scale for the whole call the multiplier applied to the elements depends only on the
   // block-scale byte (127 values): each block tabulates it once with the exact arithmetic.
   __shared__ float s_os[128];
+  // Per-expert mode: the block's 16 rows look their expert up once each (not once per thread):
+  // global scale, its guarded reciprocal and the row of the scale-factor tensor.
+  __shared__ float s_gs[kTY * kRows], s_rcp[kTY * kRows];
+  __shared__ long long s_sfrow[kTY * kRows];
   float gs_shared = 0.f;
   if (!kExperts) {
     gs_shared = gs_ptr[0];
     const int t = threadIdx.y * kTX + threadIdx.x;
     if (t < 128) s_os[t] = out_scale_of((uint8_t)t, __frcp_rn(gs_shared + (gs_shared == 0.f ? 1.0e8f : 0.f)));
+    __syncthreads();
+  } else {
+    const int t = threadIdx.y * kTX + threadIdx.x;
+    if (t < kTY * kRows) {
+      // slot t = (threadIdx.y = t / kRows, pass r = t % kRows) holds row (blockIdx.y * kTY + t / kRows) * kRows + t % kRows
+      const int64_t m = ((int64_t)blockIdx.y * kTY + t / kRows) * kRows + t % kRows;
+      float gs = 0.f;
+      long long row = m;
+      if (m < M) {
+        int lo = 0, hi = num_experts - 1;      // largest e with expert_offsets[e] <= m
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if ((int64_t)expert_offsets[mid] <= m) lo = mid;
+          else hi = mid - 1;
+        }
+        gs = gs_ptr[lo];
+        row = (long long)blockscale_offsets[lo] + (m - (long long)expert_offsets[lo]);
+      }
+      s_gs[t] = gs;
+      s_rcp[t] = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
+      s_sfrow[t] = row;
+    }
     __syncthreads();
   }
 
@@ -128,24 +154,15 @@ __global__ void __launch_bounds__(kTX* kTY)
     float gs = gs_shared;
     int64_t sf_row = m;
     if (kExperts) {
-      // largest e with expert_offsets[e] <= m
-      int lo = 0, hi = num_experts - 1;
-      if (ok) {
-        while (lo < hi) {
-          int mid = (lo + hi + 1) >> 1;
-          if ((int64_t)expert_offsets[mid] <= m) lo = mid;
-          else hi = mid - 1;
-        }
-        gs = gs_ptr[lo];
-        sf_row = (int64_t)blockscale_offsets[lo] + (m - (int64_t)expert_offsets[lo]);
-      }
+      gs = s_gs[threadIdx.y * kRows + r];
+      sf_row = s_sfrow[threadIdx.y * kRows + r];
     }
 
     float scale = __fmul_rn(gs, __fmul_rn(amax, 0.16666667163372039794921875f));  // fl32(1/6)
     scale = fminf(scale, 448.f);
     const uint8_t sfb = f32_to_e4m3(scale);
     float os;
-    if (kExperts) os = out_scale_of(sfb, __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f)));
+    if (kExperts) os = out_scale_of(sfb, s_rcp[threadIdx.y * kRows + r]);
     else os = s_os[sfb & 127];
 
     const uint32_t packed =
