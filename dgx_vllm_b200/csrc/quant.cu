@@ -72,7 +72,8 @@ template <typename T, bool kSwizzled, bool kExperts, bool kSilu>
 __global__ void __launch_bounds__(kTX* kTY)
     quantize_kernel(const T* __restrict__ x, int64_t M, int64_t K, int64_t ldx, const float* __restrict__ gs_ptr,
                     const int32_t* __restrict__ expert_offsets, const int32_t* __restrict__ blockscale_offsets,
-                    int num_experts, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+                    int num_experts, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+                    const int32_t* __restrict__ row_map, int row_div) {
   const int64_t kc = (int64_t)blockIdx.x * kTX + threadIdx.x;  // 8-element chunk index along K
   const int64_t CPR = K >> 3;
   const int64_t KB = K >> 4;
@@ -87,8 +88,16 @@ __global__ void __launch_bounds__(kTX* kTY)
     raw2[r] = make_uint4(0, 0, 0, 0);
     const int64_t m = m0 + r;
     if (col_ok && m < M) {
-      raw[r] = *reinterpret_cast<const uint4*>(x + m * ldx + kc * 8);
-      if (kSilu) raw2[r] = *reinterpret_cast<const uint4*>(x + m * ldx + K + kc * 8);
+      // optional gather: output row m is source row row_map[m] / row_div (a negative entry reads as zeros)
+      int64_t src = m;
+      if (row_map != nullptr) {
+        const int v = row_map[m];
+        src = v < 0 ? -1 : (int64_t)(v / row_div);
+      }
+      if (src >= 0) {
+        raw[r] = *reinterpret_cast<const uint4*>(x + src * ldx + kc * 8);
+        if (kSilu) raw2[r] = *reinterpret_cast<const uint4*>(x + src * ldx + K + kc * 8);
+      }
     }
   }
 
@@ -181,11 +190,11 @@ __global__ void __launch_bounds__(kTX* kTY)
 
 template <typename T, bool kSwz, bool kExp, bool kSilu>
 void launch(const void* x, int64_t M, int64_t K, int64_t ldx, const float* gs, const int32_t* eo, const int32_t* bo,
-            int ne, void* codes, void* sf, cudaStream_t st) {
+            int ne, void* codes, void* sf, cudaStream_t st, const int32_t* row_map = nullptr, int row_div = 1) {
   dim3 block(kTX, kTY);
   dim3 grid((unsigned)(((K >> 3) + kTX - 1) / kTX), (unsigned)((M + kTY * kRows - 1) / (kTY * kRows)));
   quantize_kernel<T, kSwz, kExp, kSilu><<<grid, block, 0, st>>>(reinterpret_cast<const T*>(x), M, K, ldx, gs, eo, bo,
-                                                                ne, (uint8_t*)codes, (uint8_t*)sf);
+                                                                ne, (uint8_t*)codes, (uint8_t*)sf, row_map, row_div);
 }
 
 }  // namespace
@@ -227,10 +236,10 @@ extern "C" int b200fp4_quantize(const void* x, int in_dtype, int64_t M, int64_t 
   return finish_launch(n_launch);
 }
 
-extern "C" int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,
-                                        const int32_t* expert_offsets, const int32_t* blockscale_offsets,
-                                        int32_t num_experts, int64_t sf_rows_padded, int silu_mul, void* codes,
-                                        void* sf, void* stream) {
+static int experts_quantize_impl(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,
+                                 const int32_t* expert_offsets, const int32_t* blockscale_offsets, int32_t num_experts,
+                                 int64_t sf_rows_padded, int silu_mul, void* codes, void* sf, void* stream,
+                                 const int32_t* row_map, int row_div) {
   if (M < 0 || K <= 0 || (K % 16) != 0 || num_experts <= 0 || sf_rows_padded < 0 || (sf_rows_padded % 128) != 0)
     return B200FP4_STATUS_INVALID_VALUE;
   if (in_dtype != B200FP4_DTYPE_F16 && in_dtype != B200FP4_DTYPE_BF16) return B200FP4_STATUS_NOT_SUPPORTED;
@@ -247,11 +256,28 @@ extern "C" int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, 
   const bool bf = in_dtype == B200FP4_DTYPE_BF16;
   const int64_t ldx = silu_mul ? 2 * K : K;
   if (silu_mul) {
-    if (bf) launch<__nv_bfloat16, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
-    else launch<__half, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+    if (bf) launch<__nv_bfloat16, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st, row_map, row_div);
+    else launch<__half, true, true, true>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st, row_map, row_div);
   } else {
-    if (bf) launch<__nv_bfloat16, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
-    else launch<__half, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st);
+    if (bf) launch<__nv_bfloat16, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st, row_map, row_div);
+    else launch<__half, true, true, false>(x, M, K, ldx, global_scales, expert_offsets, blockscale_offsets, num_experts, codes, sf, st, row_map, row_div);
   }
   return finish_launch(2);
+}
+
+extern "C" int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,
+                                        const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                        int32_t num_experts, int64_t sf_rows_padded, int silu_mul, void* codes,
+                                        void* sf, void* stream) {
+  return experts_quantize_impl(x, in_dtype, M, K, global_scales, expert_offsets, blockscale_offsets, num_experts,
+                               sf_rows_padded, silu_mul, codes, sf, stream, nullptr, 1);
+}
+
+extern "C" int b200fp4_experts_quantize_gather(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,
+                                               const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                               int32_t num_experts, int64_t sf_rows_padded, const int32_t* row_map,
+                                               int32_t row_div, void* codes, void* sf, void* stream) {
+  if (!row_map || row_div <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  return experts_quantize_impl(x, in_dtype, M, K, global_scales, expert_offsets, blockscale_offsets, num_experts,
+                               sf_rows_padded, 0, codes, sf, stream, row_map, row_div);
 }

@@ -87,6 +87,28 @@ def scaled_fp4_experts_quant(input_tensor, input_global_scale, expert_offsets, b
     return _experts_quant(input_tensor, input_global_scale, expert_offsets, blockscale_offsets, False)
 
 
+def shuffle_rows_scaled_fp4_experts_quant(input_tensor, dst2src_map, input_global_scale, expert_offsets, blockscale_offsets):
+    """shuffle_rows(input, dst2src_map) followed by scaled_fp4_experts_quant in one kernel: permuted row i
+    quantizes input row dst2src_map[i] (zeros for a negative entry); the [rows, K] copy is never written."""
+    dev = require_cuda(input_tensor, dst2src_map, input_global_scale, expert_offsets, blockscale_offsets)
+    require(input_tensor.dim() == 2 and input_tensor.is_contiguous(), "input must be a contiguous 2-D tensor")
+    require(input_tensor.dtype in (torch.float16, torch.bfloat16), "input must be float16 or bfloat16")
+    require(dst2src_map.dtype == torch.int32 and dst2src_map.is_contiguous(), "map must be contiguous int32")
+    rows, K = dst2src_map.numel(), input_tensor.shape[1]
+    require(K % 16 == 0, "K must be a multiple of 16")
+    E = expert_offsets.numel() - 1
+    require(input_global_scale.dtype == torch.float32 and input_global_scale.numel() >= E, "one f32 global scale per expert")
+    sf_rows = (rows + 127) // 128 * 128 + 128 * E
+    codes = torch.empty((rows, K // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty((sf_rows, (K // 16 + 3) // 4 * 4), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200fp4_experts_quantize_gather(
+            ptr(input_tensor), dtype_code(input_tensor.dtype), rows, K, ptr(input_global_scale), ptr(expert_offsets),
+            ptr(blockscale_offsets), E, sf_rows, ptr(dst2src_map), 1, ptr(codes), ptr(sf), stream_ptr(dev)),
+            "shuffle_rows_scaled_fp4_experts_quant")
+    return codes, sf.view(torch.float8_e4m3fn)
+
+
 def silu_and_mul_scaled_fp4_experts_quant(input_tensor, input_global_scale, expert_offsets, blockscale_offsets, topk=None):
     """SiLU(x[:, :K]) * x[:, K:] then per-expert NVFP4 quantization."""
     return _experts_quant(input_tensor, input_global_scale, expert_offsets, blockscale_offsets, True)
@@ -134,7 +156,7 @@ def moe_unpermute_reduce(expert_out, output_permutation, topk_weights):
 def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs,
                       a1_gs, a2_gs, expert_map=None):
     """One MoE layer over dense NVFP4 expert weights (the flow of cutlass_moe.py:567-663):
-    permute -> quantize -> grouped GEMM (gate_up) -> SiLU*up + quantize -> grouped GEMM (down) -> combine.
+    permute metadata -> gather + quantize -> grouped GEMM (gate_up) -> SiLU*up + quantize -> grouped GEMM (down) -> combine.
 
     w13_codes [E,2I,H/2], w13_sf [E, swizzled(2I,H/16)], w13_gs [E] weight global scales (448*6/amax);
     w2_* likewise for [E,H,I/2]; a1_gs / a2_gs [E] activation global scales of the two GEMM inputs."""
@@ -147,8 +169,7 @@ def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs,
     a_map = torch.empty(P, dtype=torch.int32, device=dev)
     c_map = torch.empty(P, dtype=torch.int32, device=dev)
     bso = get_cutlass_moe_mm_data(topk_ids, eo, None, None, a_map, c_map, E, N1 // 2, H, expert_map=expert_map)
-    x = shuffle_rows(hidden, a_map)
-    xq, xsf = scaled_fp4_experts_quant(x, a1_gs, eo, bso)
+    xq, xsf = shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, a1_gs, eo, bso)
     c1 = torch.empty((P, N1), dtype=hidden.dtype, device=dev)
     cutlass_fp4_moe_mm(c1, xq, w13_codes, xsf, w13_sf, (1.0 / (a1_gs * w13_gs)).float(), None, eo, bso)
     hq, hsf = silu_and_mul_scaled_fp4_experts_quant(c1, a2_gs, eo, bso)

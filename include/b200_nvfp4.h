@@ -93,6 +93,16 @@ B200FP4_API int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M,
                                          int64_t sf_rows_padded, int silu_mul, void* codes, void* sf,
                                          void* stream);
 
+/* The same with the row permutation folded in: output row m quantizes source row
+ * row_map[m] / row_div of x (a negative entry quantizes a row of zeros), i.e. shuffle_rows
+ * (vllm/_custom_ops.py:1017-1054) followed by scaled_fp4_experts_quant without the [M, K] copy in
+ * between.  x has as many rows as the map refers to. */
+B200FP4_API int b200fp4_experts_quantize_gather(const void* x, int in_dtype, int64_t M, int64_t K,
+                                                const float* global_scales, const int32_t* expert_offsets,
+                                                const int32_t* blockscale_offsets, int32_t num_experts,
+                                                int64_t sf_rows_padded, const int32_t* row_map,
+                                                int32_t row_div, void* codes, void* sf, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Part 2 -- dense block-scaled NVFP4 GEMM:  out[M,N] = alpha * (a . sfa)(b . sfb)^T.
  * Replaces cudaFP4GemmEx (declared, never defined) of cutlass_nvfp4/cuda_fp4_gemm.h:94-105 and the

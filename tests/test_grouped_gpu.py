@@ -162,3 +162,23 @@ def test_moe_prefill_layer_small():
     assert rel_err(to_np(out), ref.astype(np.float32)) < 3e-2      # a few re-quantized codes flip on bf16 rounding
     cos = float((to_np(out).ravel() @ ref.ravel()) / (np.linalg.norm(to_np(out)) * np.linalg.norm(ref)))
     assert cos > 0.999
+
+
+def test_gather_quant_matches_shuffle_then_quant():
+    from dgx_vllm_b200 import grouped_moe as gm
+    T, H, E, topk = 37, 256, 6, 3
+    g = torch.Generator().manual_seed(5)
+    hidden = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).to(torch.int32).cuda()
+    emap = torch.arange(E, dtype=torch.int32)
+    emap[2] = -1                                           # one expert is not local: its rows drop out of the map
+    P = T * topk
+    eo = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+    a_map = torch.empty(P, dtype=torch.int32, device="cuda")
+    c_map = torch.empty(P, dtype=torch.int32, device="cuda")
+    bso = gm.get_cutlass_moe_mm_data(ids, eo, None, None, a_map, c_map, E, 64, H, expert_map=emap.cuda())
+    gs = (torch.rand(E, generator=g) * 50 + 200).float().cuda()
+    c_ref, s_ref = gm.scaled_fp4_experts_quant(gm.shuffle_rows(hidden, a_map), gs, eo, bso)
+    c_new, s_new = gm.shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, gs, eo, bso)
+    assert torch.equal(c_ref, c_new)
+    assert torch.equal(s_ref.view(torch.uint8), s_new.view(torch.uint8))
