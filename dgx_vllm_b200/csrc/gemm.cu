@@ -478,6 +478,31 @@ __global__ void unpermute_reduce_kernel(const T* __restrict__ expert_out, const 
   }
 }
 
+// The same for H % 8 == 0 and 16-byte aligned rows: eight columns per thread, 16-byte loads and stores,
+// same order of additions per output element.
+template <typename T>
+__global__ void unpermute_reduce_vec8_kernel(const T* __restrict__ expert_out, const int* __restrict__ src2dst,
+                                             const float* __restrict__ topk_w, int M, int topk, int H, T* __restrict__ out) {
+  const int m = blockIdx.y;
+  const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (h >= H) return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int t = 0; t < topk; ++t) {
+    const int r = src2dst[m * topk + t];
+    if (r < 0) continue;
+    const float w = topk_w[m * topk + t];
+    const uint4 raw = *reinterpret_cast<const uint4*>(expert_out + (int64_t)r * H + h);
+    const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, to_f32<T>(v[i]), acc[i]);
+  }
+  uint4 o;
+  T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ov[i] = from_f32<T>(acc[i]);
+  *reinterpret_cast<uint4*>(out + (int64_t)m * H + h) = o;
+}
+
 // ---------------------------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -724,6 +749,18 @@ extern "C" int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, c
   if (dtype != B200FP4_DTYPE_BF16 && dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
   if (M == 0) return B200FP4_STATUS_SUCCESS;
   if (!expert_out || !src2dst || !topk_weights || !out) return B200FP4_STATUS_INVALID_VALUE;
+  if ((H % 8) == 0 && aligned(expert_out, 16) && aligned(out, 16)) {
+    dim3 grid8((unsigned)((H / 8 + 127) / 128), (unsigned)M);
+    if (dtype == B200FP4_DTYPE_BF16)
+      unpermute_reduce_vec8_kernel<__nv_bfloat16><<<grid8, 128, 0, (cudaStream_t)stream>>>(
+          reinterpret_cast<const __nv_bfloat16*>(expert_out), src2dst, topk_weights, (int)M, (int)topk, (int)H,
+          reinterpret_cast<__nv_bfloat16*>(out));
+    else
+      unpermute_reduce_vec8_kernel<__half><<<grid8, 128, 0, (cudaStream_t)stream>>>(
+          reinterpret_cast<const __half*>(expert_out), src2dst, topk_weights, (int)M, (int)topk, (int)H,
+          reinterpret_cast<__half*>(out));
+    return finish_launch(1);
+  }
   dim3 grid((unsigned)((H / 2 + 127) / 128), (unsigned)M);
   if (dtype == B200FP4_DTYPE_BF16)
     unpermute_reduce_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(
