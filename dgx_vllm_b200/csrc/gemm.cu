@@ -340,6 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // ---------------------------------------------------------------------------------------- grouped helpers
 
 constexpr int kGroupMaxExperts = 4096;
+constexpr int kPermuteGridMinPairs = 8192;   // below this one block does the whole routing pass
 
 // One block: cuts every expert's row range into 128-row tiles.
 //   hdr[0] = number of tiles; mtiles[t] = {first row, end row of the expert, A scale-tile row, expert}
@@ -446,6 +447,82 @@ __global__ void __launch_bounds__(1024)
       dst2src[pos] = p;
     }
   }
+}
+
+// The same routing metadata for large batches, as three grid-wide steps around global counters kept in
+// expert_offsets itself (no scratch): count pairs per expert, scan, scatter with expert_offsets[e] as
+// the running cursor, then shift the cursors (now each expert's end) back into start offsets.
+__global__ void moe_permute_count_kernel(const int32_t* __restrict__ topk_ids, int P,
+                                         const int32_t* __restrict__ expert_map, int global_E, int E,
+                                         int* expert_offsets, int* dst2src, int* src2dst) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+    int e = topk_ids[p];
+    if (expert_map != nullptr) e = (e >= 0 && e < global_E) ? expert_map[e] : -1;
+    if (e < 0 || e >= E) e = -1;
+    src2dst[p] = e;
+    dst2src[p] = -1;
+    if (e >= 0) atomicAdd(&expert_offsets[e], 1);
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+    moe_permute_scan_kernel(int E, int* expert_offsets, int* blockscale_offsets) {
+  __shared__ int s_scan[1024], s_scan2[1024];
+  const int tid = threadIdx.x;
+  const int per = (E + 1023) / 1024;
+  int sum = 0, sum_pad = 0;
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < E) {
+      const int c = expert_offsets[e];
+      sum += c;
+      sum_pad += (c + 127) / 128 * 128;
+    }
+  }
+  s_scan[tid] = sum;
+  s_scan2[tid] = sum_pad;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int v = tid >= d ? s_scan[tid - d] : 0, v2 = tid >= d ? s_scan2[tid - d] : 0;
+    __syncthreads();
+    s_scan[tid] += v;
+    s_scan2[tid] += v2;
+    __syncthreads();
+  }
+  int base = s_scan[tid] - sum, base_pad = s_scan2[tid] - sum_pad;
+  for (int i = 0; i < per; ++i) {
+    const int e = tid * per + i;
+    if (e < E) {
+      const int c = expert_offsets[e];
+      expert_offsets[e] = base;
+      blockscale_offsets[e] = base_pad;
+      base += c;
+      base_pad += (c + 127) / 128 * 128;
+    }
+  }
+  if (tid == 1023) {
+    expert_offsets[E] = s_scan[1023];
+    blockscale_offsets[E] = s_scan2[1023];
+  }
+}
+
+__global__ void moe_permute_scatter_kernel(int P, int* expert_offsets, int* dst2src, int* src2dst) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+    const int e = src2dst[p];
+    if (e >= 0) {
+      const int pos = atomicAdd(&expert_offsets[e], 1);
+      src2dst[p] = pos;
+      dst2src[pos] = p;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024) moe_permute_shift_kernel(int E, int* expert_offsets) {
+  __shared__ int s_end[kGroupMaxExperts];
+  for (int e = threadIdx.x; e < E; e += 1024) s_end[e] = expert_offsets[e];
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += 1024) expert_offsets[e + 1] = s_end[e];
+  if (threadIdx.x == 0) expert_offsets[0] = 0;
 }
 
 // out[i, :] = in[dst2src[i] / src_div, :] for 16-byte chunks; rows whose map entry is < 0 become zero.
@@ -724,9 +801,22 @@ extern "C" int b200fp4_moe_permute(const int32_t* topk_ids, const int32_t* exper
   if (!expert_offsets || !blockscale_offsets) return B200FP4_STATUS_INVALID_VALUE;
   if (M > 0 && (!topk_ids || !dst2src || !src2dst)) return B200FP4_STATUS_INVALID_VALUE;
   if (expert_map && global_E <= 0) return B200FP4_STATUS_INVALID_VALUE;
-  moe_permute_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(topk_ids, (int)(M * topk), expert_map, (int)global_E, (int)E,
-                                                          expert_offsets, blockscale_offsets, dst2src, src2dst);
-  return finish_launch(1);
+  const int P = (int)(M * topk);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (P < kPermuteGridMinPairs) {
+    moe_permute_kernel<<<1, 1024, 0, st>>>(topk_ids, P, expert_map, (int)global_E, (int)E, expert_offsets,
+                                           blockscale_offsets, dst2src, src2dst);
+    return finish_launch(1);
+  }
+  if (cudaMemsetAsync(expert_offsets, 0, (size_t)(E + 1) * sizeof(int32_t), st) != cudaSuccess)
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  const int blocks = std::min((P + 255) / 256, 4 * 148);
+  moe_permute_count_kernel<<<blocks, 256, 0, st>>>(topk_ids, P, expert_map, (int)global_E, (int)E, expert_offsets,
+                                                   dst2src, src2dst);
+  moe_permute_scan_kernel<<<1, 1024, 0, st>>>((int)E, expert_offsets, blockscale_offsets);
+  moe_permute_scatter_kernel<<<blocks, 256, 0, st>>>(P, expert_offsets, dst2src, src2dst);
+  moe_permute_shift_kernel<<<1, 1024, 0, st>>>((int)E, expert_offsets);
+  return finish_launch(4);
 }
 
 extern "C" int b200fp4_shuffle_rows(const void* in, int64_t row_bytes, const int32_t* dst2src, int64_t n_dst,

@@ -34,7 +34,8 @@ def get_cutlass_moe_mm_data(topk_ids, expert_offsets, problem_sizes1, problem_si
         _lib.check(L.b200fp4_moe_permute(ptr(ids), ptr(emap), 0 if emap is None else emap.numel(), M, topk, num_experts,
                                          ptr(expert_offsets), ptr(bso), ptr(input_permutation), ptr(output_permutation),
                                          stream_ptr(dev)), "get_cutlass_moe_mm_data")
-    counts = expert_offsets[1:num_experts + 1] - expert_offsets[:num_experts]
+    if problem_sizes1 is not None or problem_sizes2 is not None:
+        counts = expert_offsets[1:num_experts + 1] - expert_offsets[:num_experts]
     if problem_sizes1 is not None:
         problem_sizes1[:, 0] = counts
         problem_sizes1[:, 1] = 2 * n if is_gated else n

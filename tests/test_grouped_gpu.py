@@ -56,6 +56,32 @@ def test_permute_with_expert_map_drops_foreign_pairs():
     assert np.all(a_map[eo[-1]:] == -1)
 
 
+@pytest.mark.parametrize("with_map", [False, True])
+def test_permute_metadata_large_batch(with_map):
+    """Batches of 8192 pairs and more take the grid-wide routing pass; same contract as the one-block pass."""
+    M, E_global, topk = 2048, 96, 10
+    _, ids = _routing(M, E_global, topk, 11)
+    if with_map:
+        emap = np.full(E_global, -1, np.int32)
+        emap[np.arange(0, E_global, 2)] = np.arange(E_global // 2)
+        E = E_global // 2
+    else:
+        emap, E = None, E_global
+    eo, bso, a_map, c_map = [to_np(t) for t in _metadata(ids, E, emap)]
+    idn = ids.numpy().reshape(-1)
+    local = idn if emap is None else emap[idn]
+    counts = np.bincount(local[local >= 0], minlength=E)
+    np.testing.assert_array_equal(eo, np.concatenate([[0], np.cumsum(counts)]))
+    np.testing.assert_array_equal(bso, np.concatenate([[0], np.cumsum((counts + 127) // 128 * 128)]))
+    kept = local >= 0
+    assert np.all((c_map >= 0) == kept)
+    rows = c_map[kept]
+    assert np.all((eo[local[kept]] <= rows) & (rows < eo[local[kept] + 1]))
+    assert len(np.unique(rows)) == kept.sum()
+    np.testing.assert_array_equal(a_map[rows], np.nonzero(kept)[0] // topk)
+    assert np.all(a_map[eo[-1]:] == -1)
+
+
 def _expert_weights(E, N, K, seed):
     """dense NVFP4 expert weights quantized by the oracle: codes [E,N,K/2], linear sf [E,N,K/16], gs [E]."""
     g = torch.Generator().manual_seed(seed)
