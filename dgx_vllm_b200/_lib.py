@@ -51,6 +51,9 @@ SIGNATURES = {
     "b200fp4_fused_moe_profile_events": (None, [_vp, _vp, _vp]),
     "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                         _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_fused_moe_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200fp4_fused_sparse_moe_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
+                                             _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
 }
 
 _lib = None

@@ -1599,6 +1599,58 @@ extern "C" int b200fp4_fused_sparse_moe(const void* hidden, int h_dtype, const f
                         workspace, workspace_bytes, stream);
 }
 
+// The layer for a caller whose activations, routing and result live in HOST memory (pinned memory makes the
+// copies asynchronous): three copies in, the device entry point above, one copy out, one stream
+// synchronisation.  The device workspace holds the staging buffers in front of the layer's own workspace.
+static size_t host_stage_bytes(int64_t M, int64_t topk, int64_t H) {
+  return 2 * align_up((size_t)M * H * sizeof(__half), 256) + 2 * align_up((size_t)M * topk * sizeof(float), 256);
+}
+
+extern "C" size_t b200fp4_fused_moe_host_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E) {
+  if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
+  return host_stage_bytes(M, topk, H) + b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E);
+}
+
+extern "C" int b200fp4_fused_sparse_moe_host(const void* hidden_host, int h_dtype, const float* topk_weights_host,
+                                             const int32_t* topk_ids_host, const int32_t* expert_map, int64_t global_E,
+                                             const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
+                                             const float* w13_g, int64_t G13, const uint8_t* w2_comp,
+                                             const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g,
+                                             int64_t G2, void* out_host, int out_dtype, int64_t M, int64_t topk,
+                                             int64_t H, int64_t I, int64_t E, int flags, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+  if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (M == 0) return B200FP4_STATUS_SUCCESS;
+  if (!hidden_host || !topk_weights_host || !topk_ids_host || !out_host || !workspace)
+    return B200FP4_STATUS_INVALID_VALUE;
+  if (out_dtype != B200FP4_DTYPE_F16 && out_dtype != B200FP4_DTYPE_BF16) return B200FP4_STATUS_NOT_SUPPORTED;
+  const size_t stage = host_stage_bytes(M, topk, H);
+  if (workspace_bytes < stage) return B200FP4_STATUS_INVALID_VALUE;
+  const size_t nh = (size_t)M * H * sizeof(__half), nr = (size_t)M * topk * sizeof(float);
+  char* d_hidden = static_cast<char*>(workspace);
+  char* d_out = d_hidden + align_up(nh, 256);
+  char* d_w = d_out + align_up(nh, 256);
+  char* d_ids = d_w + align_up(nr, 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(d_ids, topk_ids_host, nr, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+      cudaMemcpyAsync(d_w, topk_weights_host, nr, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+      cudaMemcpyAsync(d_hidden, hidden_host, nh, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  const int rc = fused_moe_impl(d_hidden, H, h_dtype, reinterpret_cast<const float*>(d_w), topk,
+                                reinterpret_cast<const int32_t*>(d_ids), topk, expert_map, global_E, w13_comp, w13_meta,
+                                w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, d_out, out_dtype, M, topk, H, I,
+                                E, flags, static_cast<char*>(workspace) + stage, workspace_bytes - stage, stream);
+  if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  if (cudaMemcpyAsync(out_host, d_out, nh, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  return B200FP4_STATUS_SUCCESS;
+}
+
 // ------------------------------------------------------------------------------------------ expert parallel
 
 // One record per token: [H activations (16-bit) | topk expert ids (i32) | topk router weights (f32)].

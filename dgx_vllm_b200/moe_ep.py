@@ -156,6 +156,23 @@ class ExpertParallelMoE:
         return self._forward_cuda(hidden, topk_w, topk_ids, emap)
 
 
+    def forward_host(self, hidden_host, topk_w_host, topk_ids_host, out_host, device) -> torch.Tensor:
+        """forward for CPU tensors (pinned for asynchronous copies); out_host is valid on return.  On one GPU this
+        is a single call of the library's host-buffer entry point; with several ranks the copies bracket forward."""
+        if self.world == 1 and self._fn is None:
+            if self._bound is None:
+                from . import sparse_fp4_v7 as sp7
+                k = ("comp_T", "meta_T", "scale_T", "g_scales")
+                self._bound = sp7.FusedSparseMoE(*[self.w13[x] for x in k], *[self.w2[x] for x in k], self.inter,
+                                                 expert_map=self.expert_map(device))
+            return self._bound.forward_host(hidden_host, topk_w_host, topk_ids_host, out_host=out_host)
+        out = self.forward(hidden_host.to(device, non_blocking=True), topk_w_host.to(device, non_blocking=True),
+                           topk_ids_host.to(device, non_blocking=True))
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+        return out_host
+
+
 class ExpertParallelMoEPrefill:
     """One dense-NVFP4 MoE layer for prefill, experts sharded over the ranks of `group`.
 

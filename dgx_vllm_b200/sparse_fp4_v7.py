@@ -286,6 +286,40 @@ class FusedSparseMoE:
         return out
 
 
+    def forward_host(self, hidden_host, topk_weights_host, topk_ids_host, out_host=None,
+                     apply_router_weight_on_input: bool = False):
+        """The layer for CPU tensors: hidden [M,H] 16-bit, topk_weights [M,topk] f32, topk_ids [M,topk] i32 in host
+        memory (pinned memory keeps the copies asynchronous); returns out_host [M,H], valid on return.  One library
+        call does the three copies in, the layer, the copy out and the stream synchronisation."""
+        M, H = hidden_host.shape
+        topk = topk_ids_host.shape[1]
+        require(not hidden_host.is_cuda and not topk_weights_host.is_cuda and not topk_ids_host.is_cuda,
+                "forward_host takes CPU tensors")
+        require(H == self.H and hidden_host.is_contiguous() and hidden_host.dtype in (torch.float16, torch.bfloat16),
+                "hidden_host must be a contiguous [M,H] 16-bit tensor")
+        require(topk_weights_host.dtype == torch.float32 and topk_ids_host.dtype == torch.int32 and
+                topk_weights_host.is_contiguous() and topk_ids_host.is_contiguous() and
+                tuple(topk_weights_host.shape) == (M, topk), "topk_weights f32 / topk_ids i32 must be contiguous [M, topk]")
+        if out_host is None:
+            out_host = torch.empty((M, H), dtype=hidden_host.dtype, pin_memory=True)
+        require(not out_host.is_cuda and out_host.is_contiguous() and tuple(out_host.shape) == (M, H) and
+                out_host.dtype in (torch.float16, torch.bfloat16), "out_host must be a contiguous [M,H] 16-bit CPU tensor")
+        dev = self.device
+        key = ("host", M, topk)
+        nws = self._ws_bytes.get(key)
+        if nws is None:
+            nws = self._ws_bytes[key] = self._lib.b200fp4_fused_moe_host_workspace_bytes(M, topk, H, self.I, self.E)
+        ws = workspace(dev, nws)
+        flags = self._flags | (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0)
+        with torch.cuda.device(dev):
+            rc = self._lib.b200fp4_fused_sparse_moe_host(
+                hidden_host.data_ptr(), dtype_code(hidden_host.dtype), topk_weights_host.data_ptr(), topk_ids_host.data_ptr(),
+                *self._head, out_host.data_ptr(), dtype_code(out_host.dtype), M, topk, H, self.I, self.E, flags,
+                ws.data_ptr(), ws.numel(), stream_ptr(dev))
+        _lib.check(rc, "fused_sparse_moe_v7 (host buffers)")
+        return out_host
+
+
 def convert_weight_batch_to_v7(weights, scales, g_scales, device="cuda", batch_size=16):
     """NVFP4 expert weights -> the 2:4 tensors the ops above take, on the GPU in two launches.
 

@@ -240,6 +240,23 @@ B200FP4_API int b200fp4_fused_sparse_moe(
     int out_dtype, int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E,
     int flags, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same layer for a caller that holds activations, routing and result in HOST memory (the
+ * position of a serving process that calls the reference's op from outside the GPU framework):
+ * hidden_host, topk_weights_host, topk_ids_host and out_host are host pointers (pinned memory keeps
+ * the copies asynchronous), every other pointer is device memory as above.  Copies the three inputs
+ * to the device, runs b200fp4_fused_sparse_moe, copies the result back and synchronises the stream,
+ * so out_host is valid on return.  workspace: b200fp4_fused_moe_host_workspace_bytes(...) bytes of
+ * device memory.  out_dtype F16 or BF16. */
+B200FP4_API size_t b200fp4_fused_moe_host_workspace_bytes(int64_t M, int64_t topk, int64_t H,
+                                                          int64_t I, int64_t E);
+B200FP4_API int b200fp4_fused_sparse_moe_host(
+    const void* hidden_host, int h_dtype, const float* topk_weights_host,
+    const int32_t* topk_ids_host, const int32_t* expert_map, int64_t global_E,
+    const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
+    int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
+    const float* w2_g, int64_t G2, void* out_host, int out_dtype, int64_t M, int64_t topk, int64_t H,
+    int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Part 4 -- grouped (per-expert) NVFP4 GEMM for MoE prefill and its routing helpers.
  * The reference's own grouped kernel is an FP8 CUTLASS configuration behind

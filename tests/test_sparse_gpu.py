@@ -312,6 +312,27 @@ def test_bound_layer_object_matches_function():
         layer(hidden.cuda()[:, :512].contiguous(), tw.cuda(), ids.cuda())
 
 
+def test_bound_layer_host_buffers_match_device_call():
+    """forward_host (host pointers through the C entry point: copies in, layer, copy out, sync) gives the bytes of
+    the device call, from pinned and from pageable memory, and checks its arguments."""
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, H, I, B, topk = 16, 1024, 256, 9, 4
+    w13, w2, tw, ids, hidden = _moe_case(E, H, I, B, topk, seed=78)
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    layer = sp7.FusedSparseMoE(*c(w13), *c(w2), I)
+    ref = layer(hidden.cuda(), tw.cuda(), ids.cuda())
+    out_pageable = layer.forward_host(hidden, tw, ids, out_host=torch.empty_like(hidden))
+    assert torch.equal(out_pageable, ref.cpu())
+    out_pinned = layer.forward_host(hidden.pin_memory(), tw.pin_memory(), ids.pin_memory())
+    assert out_pinned.is_pinned() and torch.equal(out_pinned, ref.cpu())
+    ref_in = layer(hidden.cuda(), tw.cuda(), ids.cuda(), apply_router_weight_on_input=True)
+    assert torch.equal(layer.forward_host(hidden, tw, ids, apply_router_weight_on_input=True), ref_in.cpu())
+    with pytest.raises(RuntimeError):
+        layer.forward_host(hidden.cuda(), tw, ids)
+    with pytest.raises(RuntimeError):
+        layer.forward_host(hidden, tw, ids.long())
+
+
 @pytest.mark.parametrize("M,topk,E,H,I,separate", [
     (64, 8, 16, 2048, 512, False),      # 32 tokens per expert on average: eight-token passes, one launch
     (64, 8, 16, 2048, 512, True),       # ... and one launch per projection
