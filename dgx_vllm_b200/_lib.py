@@ -35,6 +35,8 @@ SIGNATURES = {
     "b200fp4_shuffle_rows": (_i32, [_vp, _i64, _vp, _i64, _i64, _vp, _vp]),
     "b200fp4_grouped_gemm_workspace_bytes": (_sz, [_i64, _i64]),
     "b200fp4_grouped_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_grouped_gemm_nvfp4_silu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64,
+                                                     _i64, _vp, _sz, _vp]),
     "b200fp4_moe_unpermute_reduce": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_sparse_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "b200fp4_sparse_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),

@@ -83,6 +83,16 @@ __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+// The quantizer's SiLU and output-scale arithmetic; shared by the stand-alone quantize kernels and the GEMM
+// epilogue that quantizes in place, so that both produce the same bytes.
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+
+// 1 / (decoded block scale / global scale), with the reference's "x == 0 -> x + 1e8" guards
+__device__ __forceinline__ float out_scale_of(uint8_t sfb, float rcp_gs) {
+  const float t = __fmul_rn(e4m3_to_f32(sfb), rcp_gs);
+  return __frcp_rn(t + (t == 0.f ? 1.0e8f : 0.f));
+}
+
 // Byte offset of scale factor (row m, k-block kb) in the padded 128x4 tile layout with KT = ceil(KB/4).
 __host__ __device__ __forceinline__ int64_t sf_swizzled_offset(int64_t m, int64_t kb, int64_t KT) {
   return ((((m >> 7) * KT + (kb >> 2)) * 32 + (m & 31)) * 4 + ((m & 127) >> 5)) * 4 + (kb & 3);

@@ -19,6 +19,8 @@
 //     the global stores, so only the ~1200-cycle drain is exposed; it moves 25 % fewer bytes per flop.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code in the status word
 // and all roles drain out, so a protocol error cannot hang the GPU.
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 
 namespace b200fp4 {
@@ -53,6 +55,11 @@ struct GemmParams {
   const int4* g_mtiles;   // per 128-row tile: {first row, end row of its expert, scale-tile row of A, expert}
   const float* g_alphas;  // [E]
   long long g_sfb_expert_bytes;
+  // fused SiLU(gate)*up + NVFP4 quantization of the result (grouped gate_up projection, N = 2*q_inter):
+  // `out` receives packed codes [rows, q_inter/2], q_sf the swizzled block scales, q_gs[E] the global scales
+  int q_inter;
+  uint8_t* q_sf;
+  const float* q_gs;
 };
 
 // What the roles need to know about one output tile.
@@ -62,16 +69,34 @@ struct TileInfo {
   int sfa_tile;     // index of the 128-row scale tile of A
   int b_row0;       // first row of the (flattened) B matrix
   int sfb_tile0;    // index of the first 128-row scale tile of B inside its expert
+  int sfb_tile1;    // ... of the second one (256-wide tiles)
+  int b_row1;       // fused SiLU tiles: first row of the "up" half of B (the gate half starts at b_row0)
   int expert;       // -1 in dense mode
   int n0;           // first output column
 };
 
-template <int BN, bool kGrouped>
+template <int BN, bool kGrouped, bool kSiluQuant = false>
 __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int m_tiles) {
   TileInfo t;
   const int mt = tile % m_tiles, nt = tile / m_tiles;
+  if (kSiluQuant) {
+    // tile nt pairs gate columns [128 nt, +128) with up columns q_inter + [128 nt, +128); n0 counts output columns
+    const int4 r = p.g_mtiles[mt];
+    t.n0 = nt * 128;
+    t.sfb_tile0 = nt;
+    t.sfb_tile1 = p.q_inter / 128 + nt;
+    t.a_row0 = r.x;
+    t.row_end = r.y;
+    t.sfa_tile = r.z;
+    t.expert = r.w;
+    t.b_row0 = r.w * p.N + nt * 128;
+    t.b_row1 = t.b_row0 + p.q_inter;
+    return t;
+  }
   t.n0 = nt * BN;
   t.sfb_tile0 = nt * (BN / 128);
+  t.sfb_tile1 = t.sfb_tile0 + 1;
+  t.b_row1 = 0;
   if (kGrouped) {
     const int4 r = p.g_mtiles[mt];
     t.a_row0 = r.x;
@@ -87,6 +112,44 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int
     t.b_row0 = nt * BN;
   }
   return t;
+}
+
+// 64 gate and 64 up values of one row (as 16-bit pairs) -> SiLU(gate)*up rounded to T -> four NVFP4 blocks:
+// 8 words of codes and 4 scale bytes, with the arithmetic of the stand-alone SiLU-mul quantizer.
+template <typename T>
+__device__ __forceinline__ void silu_quant_row(const uint32_t* pg, const uint32_t* pu, float gs, float rcp_gs,
+                                               uint32_t* codes, uint32_t& sf4) {
+#pragma unroll
+  for (int b = 0; b < 4; ++b) {
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t wg = pg[b * 8 + i], wu = pu[b * 8 + i];
+      float g0, g1, u0, u1;
+      if (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
+        g0 = __uint_as_float(wg << 16); g1 = __uint_as_float(wg & 0xFFFF0000u);
+        u0 = __uint_as_float(wu << 16); u1 = __uint_as_float(wu & 0xFFFF0000u);
+      } else {
+        const float2 fg = __half22float2(*reinterpret_cast<const __half2*>(&wg));
+        const float2 fu = __half22float2(*reinterpret_cast<const __half2*>(&wu));
+        g0 = fg.x; g1 = fg.y; u0 = fu.x; u1 = fu.y;
+      }
+      x[2 * i] = to_f32<T>(from_f32<T>(silu_f32(g0) * u0));
+      x[2 * i + 1] = to_f32<T>(from_f32<T>(silu_f32(g1) * u1));
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    float scale = __fmul_rn(gs, __fmul_rn(amax, 0.16666667163372039794921875f));
+    scale = fminf(scale, 448.f);
+    const uint8_t sfb = f32_to_e4m3(scale);
+    const float os = out_scale_of(sfb, rcp_gs);
+    codes[b * 2] = f32x8_to_e2m1(__fmul_rn(x[0], os), __fmul_rn(x[1], os), __fmul_rn(x[2], os), __fmul_rn(x[3], os),
+                                 __fmul_rn(x[4], os), __fmul_rn(x[5], os), __fmul_rn(x[6], os), __fmul_rn(x[7], os));
+    codes[b * 2 + 1] = f32x8_to_e2m1(__fmul_rn(x[8], os), __fmul_rn(x[9], os), __fmul_rn(x[10], os), __fmul_rn(x[11], os),
+                                     __fmul_rn(x[12], os), __fmul_rn(x[13], os), __fmul_rn(x[14], os), __fmul_rn(x[15], os));
+    sf4 |= (uint32_t)sfb << (8 * b);
+  }
 }
 
 // ---------------------------------------------------------------------------------------- kernel
@@ -115,7 +178,7 @@ struct Cfg {
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 };
 
-template <int BN, int KB, bool kGrouped>
+template <int BN, int KB, bool kGrouped, bool kSiluQuant = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -167,7 +230,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
-        const TileInfo ti = tile_info<BN, kGrouped>(p, tile, m_tiles);
+        const TileInfo ti = tile_info<BN, kGrouped, kSiluQuant>(p, tile, m_tiles);
         const uint8_t* sfb_base = p.sfb + (kGrouped ? (size_t)ti.expert * (size_t)p.g_sfb_expert_bytes : (size_t)0);
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1;
@@ -175,7 +238,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           unsigned char* st = smem + (size_t)s * C::kStageBytes;
           const int kblocks = min(KB, KT - ks * KB);
           int sf_tiles = 0;
-          for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((ti.sfb_tile0 + j) * 128 < p.N) ? 1 : 0;
+          for (int j = 0; j < C::kSfTiles; ++j) sf_tiles += ((j == 0 ? ti.sfb_tile0 : ti.sfb_tile1) * 128 < p.N) ? 1 : 0;
           // the small scale-factor copies go first and on their own barrier, so the scale warps can
           // move them into tensor memory while the operand tiles are still in flight
           const uint32_t sbar = smem_u32(&sf_full[s]);
@@ -184,11 +247,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                        (uint32_t)kblocks * 512, sbar);
           for (int j = 0; j < sf_tiles; ++j)
             bulk_load_1d(smem_u32(st + C::kStageA + C::kStageB + C::kStageSFA + j * (KB * 512)),
-                         sfb_base + ((size_t)(ti.sfb_tile0 + j) * KT + (size_t)ks * KB) * 512, (uint32_t)kblocks * 512, sbar);
+                         sfb_base + ((size_t)(j == 0 ? ti.sfb_tile0 : ti.sfb_tile1) * KT + (size_t)ks * KB) * 512,
+                         (uint32_t)kblocks * 512, sbar);
           const uint32_t bar = smem_u32(&full_bar[s]);
           mbar_expect_tx(bar, (uint32_t)(C::kStageA + C::kStageB));
           tma_load_2d(smem_u32(st), &map_a, ks * C::kRowBytes, ti.a_row0, bar);
-          tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
+          if (kSiluQuant) {
+            // map_b's box is 128 rows here: the gate rows and the up rows of the tile land one after the other
+            tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
+            tma_load_2d(smem_u32(st + C::kStageA + 128 * C::kRowBytes), &map_b, ks * C::kRowBytes, ti.b_row1, bar);
+          } else {
+            tma_load_2d(smem_u32(st + C::kStageA), &map_b, ks * C::kRowBytes, ti.b_row0, bar);
+          }
         }
       }
     }
@@ -265,7 +335,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++tcount) {
-      const TileInfo ti = tile_info<BN, kGrouped>(p, tile, m_tiles);
+      const TileInfo ti = tile_info<BN, kGrouped, kSiluQuant>(p, tile, m_tiles);
       const float alpha = kGrouped ? p.g_alphas[ti.expert] : alpha_dense;
       const uint32_t acc = tcount % C::kAcc, aph = (tcount / C::kAcc) & 1;
       ok = mbar_wait(smem_u32(&acc_full[acc]), aph, p.status, 4);
@@ -274,6 +344,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tcgen05_fence_after();
       const int row = ti.a_row0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if constexpr (kSiluQuant) {
+        // Tensor-memory columns [0,128) hold the gate half of this thread's row, [128,256) the up half.
+        // This warp takes 64 of the 128 output columns: 4 blocks of 16 -> 32 bytes of codes + 4 scale bytes,
+        // computed exactly as the separate SiLU-mul quantizer does from the 16-bit rounded GEMM output.
+        const int half = warp >= 10 ? 1 : 0;
+        const float gs = p.q_gs[ti.expert];
+        const float rcp_gs = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
+        // drain both halves as 16-bit pairs (the rounding the separate GEMM's output has), hand the accumulator
+        // back, and only then do the SiLU / quantization arithmetic, so that it overlaps the next tile's main loop
+        uint32_t pg[32], pu[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rg[32], ru[32];
+          tcgen05_ld_32x32(taddr + (half * 2 + c) * 32, rg);
+          tcgen05_ld_32x32(taddr + 128 + (half * 2 + c) * 32, ru);
+          tcgen05_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float g0 = __uint_as_float(rg[2 * i]) * alpha, g1 = __uint_as_float(rg[2 * i + 1]) * alpha;
+            const float u0 = __uint_as_float(ru[2 * i]) * alpha, u1 = __uint_as_float(ru[2 * i + 1]) * alpha;
+            if (p.out_bf16) {
+              const __nv_bfloat162 vg = __floats2bfloat162_rn(g0, g1), vu = __floats2bfloat162_rn(u0, u1);
+              pg[c * 16 + i] = *reinterpret_cast<const uint32_t*>(&vg);
+              pu[c * 16 + i] = *reinterpret_cast<const uint32_t*>(&vu);
+            } else {
+              const __half2 vg = __floats2half2_rn(g0, g1), vu = __floats2half2_rn(u0, u1);
+              pg[c * 16 + i] = *reinterpret_cast<const uint32_t*>(&vg);
+              pu[c * 16 + i] = *reinterpret_cast<const uint32_t*>(&vu);
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+        // rows past the end of the expert are never stored: warps whose 32 rows are all past it skip the arithmetic
+        if (row < ti.row_end) {
+          uint32_t codes[8];
+          uint32_t sf4 = 0;
+          if (p.out_bf16) silu_quant_row<__nv_bfloat16>(pg, pu, gs, rcp_gs, codes, sf4);
+          else silu_quant_row<__half>(pg, pu, gs, rcp_gs, codes, sf4);
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (size_t)row * (size_t)(p.q_inter / 2) + (ti.n0 + half * 64) / 2;
+          st_global_v8(dst, codes);
+          const size_t kt2 = (size_t)(p.q_inter / 64);
+          *reinterpret_cast<uint32_t*>(p.q_sf + ((size_t)ti.sfa_tile * kt2 + (size_t)(ti.n0 / 64 + half)) * 512 + lane * 16 +
+                                       quarter * 4) = sf4;
+        }
+        continue;
+      }
       // drain this thread's row of the accumulator into packed 16-bit registers ...
       uint32_t packed[BN / 4];
 #pragma unroll
@@ -616,25 +734,25 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_by
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int KB, bool kGrouped>
+template <int BN, int KB, bool kGrouped, bool kSiluQuant = false>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int max_m_tiles, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, KB, kGrouped>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, KB, kGrouped, kSiluQuant>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)Cfg<BN, KB>::kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
     attr_set[dev] = true;
   }
-  p.n_tiles = (p.N + BN - 1) / BN;
+  p.n_tiles = kSiluQuant ? p.q_inter / 128 : (p.N + BN - 1) / BN;
   long long grid = (long long)max_m_tiles * p.n_tiles;
   if (grid > sm_count()) grid = sm_count();
   if (grid < 1) grid = 1;
   p.k_stages = (p.K + KB * 64 - 1) / (KB * 64);
-  nvfp4_gemm_kernel<BN, KB, kGrouped><<<(unsigned)grid, kGemmThreads, Cfg<BN, KB>::kSmemBytes, st>>>(ma, mb, p);
+  nvfp4_gemm_kernel<BN, KB, kGrouped, kSiluQuant><<<(unsigned)grid, kGemmThreads, Cfg<BN, KB>::kSmemBytes, st>>>(ma, mb, p);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -742,10 +860,14 @@ extern "C" size_t b200fp4_grouped_gemm_workspace_bytes(int64_t rows_capacity, in
   return 256 + (size_t)(rows_capacity / kBM + E + 1) * sizeof(int4);
 }
 
-extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf,
-                                          const float* alphas, const int32_t* expert_offsets, const int32_t* sf_offsets,
-                                          void* out, int out_dtype, int64_t rows_capacity, int64_t N, int64_t K, int64_t E,
-                                          int tile_n, void* workspace, size_t workspace_bytes, void* stream) {
+// q_sf / q_gs non-null: the gate_up projection with SiLU(gate)*up and the NVFP4 quantization of the result in the
+// epilogue (out = packed codes [rows_capacity, N/4]).
+static int grouped_gemm_impl(const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf,
+                             const float* alphas, const int32_t* expert_offsets, const int32_t* sf_offsets, void* out,
+                             int out_dtype, int64_t rows_capacity, int64_t N, int64_t K, int64_t E, int tile_n,
+                             void* workspace, size_t workspace_bytes, void* stream, void* q_sf, const float* q_gs) {
+  const bool fused = q_sf != nullptr;
+  if (fused && (!q_gs || (N % 256) != 0 || !aligned(out, 32) || !aligned(q_sf, 4))) return B200FP4_STATUS_INVALID_VALUE;
   if (rows_capacity < 0 || N <= 0 || K <= 0 || E <= 0 || (K % 64) != 0) return B200FP4_STATUS_INVALID_VALUE;
   if (out_dtype != B200FP4_DTYPE_BF16 && out_dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
   if (rows_capacity == 0) return B200FP4_STATUS_SUCCESS;
@@ -757,6 +879,7 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   if (E > kGroupMaxExperts || rows_capacity > (1 << 24) || N > (1 << 20) || K > (1 << 24) || E * N > (int64_t)1 << 30)
     return B200FP4_STATUS_NOT_SUPPORTED;
   if (tile_n != 0 && tile_n != 128 && tile_n != 256) return B200FP4_STATUS_INVALID_VALUE;
+  if (fused && tile_n == 128) return B200FP4_STATUS_INVALID_VALUE;
   if (!workspace || !aligned(workspace, 16) || workspace_bytes < b200fp4_grouped_gemm_workspace_bytes(rows_capacity, E))
     return B200FP4_STATUS_ALLOC_FAILED;
   if (b200fp4_has_hardware_acceleration() != 1) return B200FP4_STATUS_ARCH_MISMATCH;
@@ -775,13 +898,17 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   p.g_mtiles = reinterpret_cast<const int4*>(reinterpret_cast<unsigned char*>(workspace) + 256);
   p.g_alphas = alphas;
   p.g_sfb_expert_bytes = (long long)b200fp4_sf_swizzled_bytes(N, K / 16);
+  p.q_inter = fused ? (int)(N / 2) : 0;
+  p.q_sf = reinterpret_cast<uint8_t*>(q_sf);
+  p.q_gs = q_gs;
   // short K means short main loops: prefer the double-buffered narrow tile there
   int bn = tile_n;
   if (bn == 0) bn = (K >= 2048 && N % 256 == 0) ? 256 : 128;
+  if (fused) bn = 256;
   const int kb = stage_kblocks();
   CUtensorMap ma, mb;
   if (!make_map(&ma, a_codes, (uint64_t)rows_capacity, (uint64_t)K / 2, kBM, kb * 32) ||
-      !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, (uint32_t)bn, kb * 32))
+      !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, fused ? 128u : (uint32_t)bn, kb * 32))
     return B200FP4_STATUS_INTERNAL_ERROR;
   if (cudaMemsetAsync(workspace, 0, 32, st) != cudaSuccess) {
     cudaGetLastError();
@@ -789,9 +916,28 @@ extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_cod
   }
   grouped_tiles_kernel<<<1, 1024, 0, st>>>(expert_offsets, sf_offsets, (int)E, const_cast<int*>(p.g_hdr),
                                            const_cast<int4*>(p.g_mtiles), max_tiles);
-  int rc = dispatch_gemm<true>(bn, kb, ma, mb, p, max_tiles, st);
+  int rc = fused ? launch_gemm<256, 4, true, true>(ma, mb, p, max_tiles, st) : dispatch_gemm<true>(bn, kb, ma, mb, p, max_tiles, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return finish_launch(3);
+}
+
+extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf,
+                                          const float* alphas, const int32_t* expert_offsets, const int32_t* sf_offsets,
+                                          void* out, int out_dtype, int64_t rows_capacity, int64_t N, int64_t K, int64_t E,
+                                          int tile_n, void* workspace, size_t workspace_bytes, void* stream) {
+  return grouped_gemm_impl(a_codes, b_codes, a_sf, b_sf, alphas, expert_offsets, sf_offsets, out, out_dtype, rows_capacity,
+                           N, K, E, tile_n, workspace, workspace_bytes, stream, nullptr, nullptr);
+}
+
+extern "C" int b200fp4_grouped_gemm_nvfp4_silu_quant(const void* a_codes, const void* b_codes, const void* a_sf,
+                                                     const void* b_sf, const float* alphas, const int32_t* expert_offsets,
+                                                     const int32_t* sf_offsets, const float* out_global_scales,
+                                                     int mid_dtype, void* out_codes, void* out_sf, int64_t rows_capacity,
+                                                     int64_t N, int64_t K, int64_t E, void* workspace,
+                                                     size_t workspace_bytes, void* stream) {
+  if (!out_sf || !out_global_scales) return B200FP4_STATUS_INVALID_VALUE;
+  return grouped_gemm_impl(a_codes, b_codes, a_sf, b_sf, alphas, expert_offsets, sf_offsets, out_codes, mid_dtype,
+                           rows_capacity, N, K, E, 0, workspace, workspace_bytes, stream, out_sf, out_global_scales);
 }
 
 extern "C" int b200fp4_moe_permute(const int32_t* topk_ids, const int32_t* expert_map, int64_t global_E, int64_t M,

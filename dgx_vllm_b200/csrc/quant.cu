@@ -58,14 +58,6 @@ __device__ __forceinline__ float amax8(const uint4& raw) {
   return fmaxf(Pk<T>::lo(w), Pk<T>::hi(w));
 }
 
-__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
-
-// 1 / (decoded block scale / global scale), with the reference's "x == 0 -> x + 1e8" guards
-__device__ __forceinline__ float out_scale_of(uint8_t sfb, float rcp_gs) {
-  const float t = __fmul_rn(e4m3_to_f32(sfb), rcp_gs);
-  return __frcp_rn(t + (t == 0.f ? 1.0e8f : 0.f));
-}
-
 // kExperts: per-row expert lookup (global scale + scale-factor row offset per expert).
 // kSilu:    input is [M, 2K]; quantize round_to_T(silu(x[:, :K]) * x[:, K:]).
 template <typename T, bool kSwizzled, bool kExperts, bool kSilu>

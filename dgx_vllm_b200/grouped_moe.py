@@ -140,6 +140,39 @@ def cutlass_fp4_moe_mm(out_tensors, a_tensors, b_tensors, a_scales, b_scales, al
     return out_tensors
 
 
+def cutlass_fp4_moe_mm_silu_and_mul_quant(a_tensors, b_tensors, a_scales, b_scales, alphas, expert_offsets, sf_offsets,
+                                          out_global_scale, mid_dtype=torch.bfloat16):
+    """cutlass_fp4_moe_mm into a [rows, 2I] tensor of mid_dtype followed by
+    silu_and_mul_scaled_fp4_experts_quant, in one kernel: the gate_up projection's epilogue applies
+    SiLU(gate)*up to the 16-bit rounded products and quantizes them, so the [rows, 2I] tensor is never
+    written.  b_tensors [E, 2I, K/2] with the gate rows first (I a multiple of 128).  Returns
+    (codes [rows, I/2], swizzled scales) with the bytes the two separate ops give for every valid row."""
+    dev = require_cuda(a_tensors, b_tensors, a_scales, b_scales, alphas, expert_offsets, sf_offsets, out_global_scale)
+    require(a_tensors.dim() == 2 and b_tensors.dim() == 3, "a [rows,K/2], b [E,2I,K/2]")
+    rows, K2 = a_tensors.shape
+    E, N, K2b = b_tensors.shape
+    require(K2 == K2b and a_tensors.is_contiguous() and b_tensors.is_contiguous(), "a and b must share K and be contiguous")
+    require(N % 256 == 0, "the intermediate size must be a multiple of 128")
+    require(alphas.dtype == torch.float32 and alphas.numel() >= E, "one f32 alpha per expert")
+    require(out_global_scale.dtype == torch.float32 and out_global_scale.numel() >= E, "one f32 global scale per expert")
+    require(expert_offsets.dtype == torch.int32 and sf_offsets.dtype == torch.int32, "offsets must be int32")
+    require(mid_dtype in (torch.float16, torch.bfloat16), "mid_dtype must be float16 or bfloat16")
+    L = _lib.lib()
+    K, I = K2 * 2, N // 2
+    require(b_scales.numel() * b_scales.element_size() >= E * L.b200fp4_sf_swizzled_bytes(N, K // 16),
+            "b_scales must hold one swizzled scale tensor per expert")
+    sf_rows = (rows + 127) // 128 * 128 + 128 * E
+    codes = torch.empty((rows, I // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty((sf_rows, (I // 16 + 3) // 4 * 4), dtype=torch.uint8, device=dev)
+    ws = workspace(dev, L.b200fp4_grouped_gemm_workspace_bytes(rows, E))
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_grouped_gemm_nvfp4_silu_quant(
+            ptr(a_tensors), ptr(b_tensors), ptr(a_scales), ptr(b_scales), ptr(alphas), ptr(expert_offsets), ptr(sf_offsets),
+            ptr(out_global_scale), dtype_code(mid_dtype), ptr(codes), ptr(sf), rows, N, K, E, ptr(ws), ws.numel(),
+            stream_ptr(dev)), "cutlass_fp4_moe_mm_silu_and_mul_quant")
+    return codes, sf.view(torch.float8_e4m3fn)
+
+
 def moe_unpermute_reduce(expert_out, output_permutation, topk_weights):
     """out[m] = sum_t topk_weights[m,t] * expert_out[output_permutation[m*topk+t]] over local pairs."""
     dev = require_cuda(expert_out, output_permutation, topk_weights)
@@ -157,7 +190,8 @@ def moe_unpermute_reduce(expert_out, output_permutation, topk_weights):
 def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs,
                       a1_gs, a2_gs, expert_map=None):
     """One MoE layer over dense NVFP4 expert weights (the flow of cutlass_moe.py:567-663):
-    permute metadata -> gather + quantize -> grouped GEMM (gate_up) -> SiLU*up + quantize -> grouped GEMM (down) -> combine.
+    permute metadata -> gather + quantize -> grouped GEMM (gate_up) with SiLU*up + quantize in its epilogue ->
+    grouped GEMM (down) -> combine.
 
     w13_codes [E,2I,H/2], w13_sf [E, swizzled(2I,H/16)], w13_gs [E] weight global scales (448*6/amax);
     w2_* likewise for [E,H,I/2]; a1_gs / a2_gs [E] activation global scales of the two GEMM inputs."""
@@ -171,9 +205,13 @@ def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs,
     c_map = torch.empty(P, dtype=torch.int32, device=dev)
     bso = get_cutlass_moe_mm_data(topk_ids, eo, None, None, a_map, c_map, E, N1 // 2, H, expert_map=expert_map)
     xq, xsf = shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, a1_gs, eo, bso)
-    c1 = torch.empty((P, N1), dtype=hidden.dtype, device=dev)
-    cutlass_fp4_moe_mm(c1, xq, w13_codes, xsf, w13_sf, (1.0 / (a1_gs * w13_gs)).float(), None, eo, bso)
-    hq, hsf = silu_and_mul_scaled_fp4_experts_quant(c1, a2_gs, eo, bso)
+    alpha1 = (1.0 / (a1_gs * w13_gs)).float()
+    if N1 % 256 == 0:
+        hq, hsf = cutlass_fp4_moe_mm_silu_and_mul_quant(xq, w13_codes, xsf, w13_sf, alpha1, eo, bso, a2_gs, hidden.dtype)
+    else:
+        c1 = torch.empty((P, N1), dtype=hidden.dtype, device=dev)
+        cutlass_fp4_moe_mm(c1, xq, w13_codes, xsf, w13_sf, alpha1, None, eo, bso)
+        hq, hsf = silu_and_mul_scaled_fp4_experts_quant(c1, a2_gs, eo, bso)
     c2 = torch.empty((P, H), dtype=hidden.dtype, device=dev)
     cutlass_fp4_moe_mm(c2, hq, w2_codes, hsf, w2_sf, (1.0 / (a2_gs * w2_gs)).float(), None, eo, bso)
     return moe_unpermute_reduce(c2, c_map, topk_weights)

@@ -295,6 +295,20 @@ B200FP4_API int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_co
                                            int64_t K, int64_t E, int tile_n, void* workspace,
                                            size_t workspace_bytes, void* stream);
 
+/* The gate_up projection of a gated MoE layer with the activation and the next quantization in the
+ * GEMM's epilogue: cutlass_fp4_group_mm into a [rows, N] tensor of mid_dtype followed by
+ * silu_and_mul_scaled_fp4_experts_quant (vllm/_custom_ops.py:1706-1733), without writing that tensor.
+ * b [E, N, K/2] holds the gate rows [0, N/2) before the up rows [N/2, N) (N/2 a multiple of 128).
+ * Each product is scaled by alphas[e] and rounded to mid_dtype (F16/BF16), SiLU(gate)*up is rounded to
+ * mid_dtype, and blocks of 16 are quantized with out_global_scales[e]: out_codes [rows_capacity, N/4]
+ * (32-byte aligned) and out_sf, swizzled with expert e's rows at sf_offsets[e], receive the same bytes
+ * as the two separate calls for every row below expert_offsets[E]; other rows are not written. */
+B200FP4_API int b200fp4_grouped_gemm_nvfp4_silu_quant(
+    const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf, const float* alphas,
+    const int32_t* expert_offsets, const int32_t* sf_offsets, const float* out_global_scales,
+    int mid_dtype, void* out_codes, void* out_sf, int64_t rows_capacity, int64_t N, int64_t K,
+    int64_t E, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Un-permute and router-weighted sum: out[m,:] = sum_t w[m,t] * expert_out[src2dst[m*topk+t], :]
  * over local pairs (the shuffle_rows + weighted sum at the end of
  * vllm/model_executor/layers/fused_moe/experts/cutlass_moe.py:567-663). */

@@ -134,6 +134,45 @@ def test_experts_quant_and_grouped_gemm(M, E, topk, N, K, tile_n):
     assert rel_err(to_np(out), ref) < TOL
 
 
+@pytest.mark.parametrize("M,E,topk,I,K,dtype", [
+    (300, 8, 4, 128, 256, torch.bfloat16),      # experts with more than one 128-row tile, one output tile per row tile
+    (64, 4, 2, 256, 2048, torch.bfloat16),      # several k stages, two output tiles per row tile
+    (50, 16, 3, 512, 512, torch.float16),       # some experts without rows; f16 intermediate
+])
+def test_grouped_gemm_with_silu_quant_epilogue_matches_separate_ops(M, E, topk, I, K, dtype):
+    """gate_up GEMM with SiLU*up + quantization in its epilogue == GEMM into a 16-bit tensor, then the
+    SiLU-mul quantizer: identical codes and block scales for every valid row."""
+    from dgx_vllm_b200 import grouped_moe as gm
+    from dgx_vllm_b200.ops import last_gemm_status
+    _, ids = _routing(M, E, topk, M + I)
+    eo, bso, a_map, c_map = _metadata(ids, E)
+    hidden = torch.randn(M, K, generator=torch.Generator().manual_seed(5)).to(dtype)
+    a_gs = torch.linspace(50.0, 400.0, E).cuda()
+    a2_gs = torch.linspace(300.0, 30.0, E).cuda()
+    xq, xsf = gm.shuffle_rows_scaled_fp4_experts_quant(hidden.cuda(), a_map, a_gs, eo, bso)
+    wc, wsf, wgs = _expert_weights(E, 2 * I, K, 9)
+    wc_d, wsf_d = torch.from_numpy(wc).cuda(), torch.from_numpy(_swizzle_experts(wsf)).cuda()
+    alphas = (1.0 / (a_gs * torch.from_numpy(wgs).cuda())).float()
+    c1 = torch.zeros((M * topk, 2 * I), dtype=dtype, device="cuda")
+    gm.cutlass_fp4_moe_mm(c1, xq, wc_d, xsf, wsf_d, alphas, None, eo, bso)
+    ref_q, ref_sf = gm.silu_and_mul_scaled_fp4_experts_quant(c1, a2_gs, eo, bso)
+    got_q, got_sf = gm.cutlass_fp4_moe_mm_silu_and_mul_quant(xq, wc_d, xsf, wsf_d, alphas, eo, bso, a2_gs, dtype)
+    assert last_gemm_status() == 0
+    eon, bson = to_np(eo), to_np(bso)
+    rows = eon[-1]
+    np.testing.assert_array_equal(to_np(got_q)[:rows], to_np(ref_q)[:rows])
+    g, r = to_np(got_sf).reshape(-1), to_np(ref_sf).reshape(-1)
+    KB = I // 16
+    row_bytes = (KB + 3) // 4 * 4
+    for e in range(E):
+        n = eon[e + 1] - eon[e]
+        if n == 0:
+            continue
+        pad = (n + 127) // 128 * 128
+        sl = slice(bson[e] * row_bytes, (bson[e] + pad) * row_bytes)
+        np.testing.assert_array_equal(oracle.sf_swizzled_to_linear(g[sl], n, KB), oracle.sf_swizzled_to_linear(r[sl], n, KB))
+
+
 def test_silu_quant_and_unpermute():
     from dgx_vllm_b200 import grouped_moe as gm
     M, E, topk, I = 30, 4, 2, 128
