@@ -29,6 +29,8 @@ SIGNATURES = {
     "b200fp4_quantize": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "b200fp4_experts_quantize": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp]),
     "b200fp4_experts_quantize_gather": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _vp, _vp, _vp]),
+    "b200fp4_experts_quantize_scatter": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _vp, _i64,
+                                              _vp, _vp, _vp]),
     "b200fp4_gemm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "b200fp4_gemm_nvfp4": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_moe_permute": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]),

@@ -570,16 +570,29 @@ __global__ void __launch_bounds__(1024)
 // The same routing metadata for large batches, as three grid-wide steps around global counters kept in
 // expert_offsets itself (no scratch): count pairs per expert, scan, scatter with expert_offsets[e] as
 // the running cursor, then shift the cursors (now each expert's end) back into start offsets.
-__global__ void moe_permute_count_kernel(const int32_t* __restrict__ topk_ids, int P,
-                                         const int32_t* __restrict__ expert_map, int global_E, int E,
-                                         int* expert_offsets, int* dst2src, int* src2dst) {
-  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
+// Both grid-wide passes aggregate per block in shared memory first: with skewed routing a popular expert would
+// otherwise take one global atomic per pair on a single address.
+constexpr int kPermuteBlock = 1024;
+
+__global__ void __launch_bounds__(kPermuteBlock)
+    moe_permute_count_kernel(const int32_t* __restrict__ topk_ids, int P, const int32_t* __restrict__ expert_map,
+                             int global_E, int E, int* expert_offsets, int* dst2src, int* src2dst) {
+  __shared__ int s_count[kGroupMaxExperts];
+  for (int e = threadIdx.x; e < E; e += kPermuteBlock) s_count[e] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kPermuteBlock + threadIdx.x;
+  if (p < P) {
     int e = topk_ids[p];
     if (expert_map != nullptr) e = (e >= 0 && e < global_E) ? expert_map[e] : -1;
     if (e < 0 || e >= E) e = -1;
     src2dst[p] = e;
     dst2src[p] = -1;
-    if (e >= 0) atomicAdd(&expert_offsets[e], 1);
+    if (e >= 0) atomicAdd(&s_count[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kPermuteBlock) {
+    const int c = s_count[e];
+    if (c > 0) atomicAdd(&expert_offsets[e], c);
   }
 }
 
@@ -624,14 +637,27 @@ __global__ void __launch_bounds__(1024)
   }
 }
 
-__global__ void moe_permute_scatter_kernel(int P, int* expert_offsets, int* dst2src, int* src2dst) {
-  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < P; p += gridDim.x * blockDim.x) {
-    const int e = src2dst[p];
-    if (e >= 0) {
-      const int pos = atomicAdd(&expert_offsets[e], 1);
-      src2dst[p] = pos;
-      dst2src[pos] = p;
-    }
+__global__ void __launch_bounds__(kPermuteBlock)
+    moe_permute_scatter_kernel(int P, int E, int* expert_offsets, int* dst2src, int* src2dst) {
+  __shared__ int s_count[kGroupMaxExperts];     // pairs of this block per expert, then the block's first row
+  for (int e = threadIdx.x; e < E; e += kPermuteBlock) s_count[e] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kPermuteBlock + threadIdx.x;
+  int e = -1, rank = 0;
+  if (p < P) {
+    e = src2dst[p];
+    if (e >= 0) rank = atomicAdd(&s_count[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += kPermuteBlock) {
+    const int c = s_count[i];
+    if (c > 0) s_count[i] = atomicAdd(&expert_offsets[i], c);
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int pos = s_count[e] + rank;
+    src2dst[p] = pos;
+    dst2src[pos] = p;
   }
 }
 
@@ -956,11 +982,11 @@ extern "C" int b200fp4_moe_permute(const int32_t* topk_ids, const int32_t* exper
   }
   if (cudaMemsetAsync(expert_offsets, 0, (size_t)(E + 1) * sizeof(int32_t), st) != cudaSuccess)
     return B200FP4_STATUS_EXECUTION_FAILED;
-  const int blocks = std::min((P + 255) / 256, 4 * 148);
-  moe_permute_count_kernel<<<blocks, 256, 0, st>>>(topk_ids, P, expert_map, (int)global_E, (int)E, expert_offsets,
-                                                   dst2src, src2dst);
+  const int blocks = (P + kPermuteBlock - 1) / kPermuteBlock;
+  moe_permute_count_kernel<<<blocks, kPermuteBlock, 0, st>>>(topk_ids, P, expert_map, (int)global_E, (int)E,
+                                                             expert_offsets, dst2src, src2dst);
   moe_permute_scan_kernel<<<1, 1024, 0, st>>>((int)E, expert_offsets, blockscale_offsets);
-  moe_permute_scatter_kernel<<<blocks, 256, 0, st>>>(P, expert_offsets, dst2src, src2dst);
+  moe_permute_scatter_kernel<<<blocks, kPermuteBlock, 0, st>>>(P, (int)E, expert_offsets, dst2src, src2dst);
   moe_permute_shift_kernel<<<1, 1024, 0, st>>>((int)E, expert_offsets);
   return finish_launch(4);
 }

@@ -180,6 +180,85 @@ __global__ void __launch_bounds__(kTX* kTY)
   }
 }
 
+// Token-major form of the gather above: block t reads source row t once and quantizes it for each of its
+// `topk` destination rows src2dst[t*topk + s] (negative = no destination), each with the global scale of the
+// expert that owns the destination row.  Same bytes as quantizing the gathered rows one by one; the source is
+// read once instead of topk times.
+constexpr int kScatterMaxTopk = 32;
+constexpr int kScatterThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kScatterThreads)
+    experts_quantize_scatter_kernel(const T* __restrict__ x, int64_t K, int topk, const int32_t* __restrict__ src2dst,
+                                    const float* __restrict__ gs_ptr, const int32_t* __restrict__ expert_offsets,
+                                    const int32_t* __restrict__ blockscale_offsets, int num_experts,
+                                    const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+                                    int global_E, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+  __shared__ float s_gs[kScatterMaxTopk], s_rcp[kScatterMaxTopk];
+  __shared__ long long s_sfrow[kScatterMaxTopk];
+  __shared__ int s_dst[kScatterMaxTopk];
+  const int64_t t = blockIdx.x;
+  const int64_t CPR = K >> 3, KB = K >> 4, KT = (KB + 3) >> 2;
+  // the first chunk of the row is requested before the destination lookup, so the two latencies overlap
+  uint4 raw_first = make_uint4(0, 0, 0, 0);
+  if ((int64_t)threadIdx.x < CPR) raw_first = *reinterpret_cast<const uint4*>(x + t * K + (int64_t)threadIdx.x * 8);
+  if ((int)threadIdx.x < topk) {
+    const int dst = src2dst[t * topk + threadIdx.x];
+    float gs = 0.f;
+    long long row = 0;
+    if (dst >= 0) {
+      int lo;
+      if (topk_ids != nullptr) {
+        // the pair's routing entry names the expert directly
+        lo = topk_ids[t * topk + threadIdx.x];
+        if (expert_map != nullptr) lo = (lo >= 0 && lo < global_E) ? expert_map[lo] : 0;
+        lo = min(max(lo, 0), num_experts - 1);
+      } else {
+        lo = 0;
+        int hi = num_experts - 1;            // largest e with expert_offsets[e] <= dst
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (expert_offsets[mid] <= dst) lo = mid;
+          else hi = mid - 1;
+        }
+      }
+      gs = gs_ptr[lo];
+      row = (long long)blockscale_offsets[lo] + (dst - expert_offsets[lo]);
+    }
+    s_dst[threadIdx.x] = dst;
+    s_gs[threadIdx.x] = gs;
+    s_rcp[threadIdx.x] = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
+    s_sfrow[threadIdx.x] = row;
+  }
+  __syncthreads();
+  for (int64_t base = 0; base < CPR; base += kScatterThreads) {
+    const int64_t kc = base + threadIdx.x;
+    const bool ok = kc < CPR;
+    uint4 raw = raw_first;
+    if (base > 0) {
+      raw = make_uint4(0, 0, 0, 0);
+      if (ok) raw = *reinterpret_cast<const uint4*>(x + t * K + kc * 8);
+    }
+    float amax = amax8<T>(raw);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    float v[8];
+    unpack8<T>(raw, v);
+    const float sixth = __fmul_rn(amax, 0.16666667163372039794921875f);
+    for (int sl = 0; sl < topk; ++sl) {
+      const int dst = s_dst[sl];
+      if (dst < 0 || !ok) continue;
+      const float scale = fminf(__fmul_rn(s_gs[sl], sixth), 448.f);
+      const uint8_t sfb = f32_to_e4m3(scale);
+      const float os = out_scale_of(sfb, s_rcp[sl]);
+      const uint32_t packed =
+          f32x8_to_e2m1(__fmul_rn(v[0], os), __fmul_rn(v[1], os), __fmul_rn(v[2], os), __fmul_rn(v[3], os),
+                        __fmul_rn(v[4], os), __fmul_rn(v[5], os), __fmul_rn(v[6], os), __fmul_rn(v[7], os));
+      *reinterpret_cast<uint32_t*>(codes + (int64_t)dst * (K >> 1) + kc * 4) = packed;
+      if ((kc & 1) == 0) sf[sf_swizzled_offset(s_sfrow[sl], kc >> 1, KT)] = sfb;
+    }
+  }
+}
+
 template <typename T, bool kSwz, bool kExp, bool kSilu>
 void launch(const void* x, int64_t M, int64_t K, int64_t ldx, const float* gs, const int32_t* eo, const int32_t* bo,
             int ne, void* codes, void* sf, cudaStream_t st, const int32_t* row_map = nullptr, int row_div = 1) {
@@ -263,6 +342,38 @@ extern "C" int b200fp4_experts_quantize(const void* x, int in_dtype, int64_t M, 
                                         void* sf, void* stream) {
   return experts_quantize_impl(x, in_dtype, M, K, global_scales, expert_offsets, blockscale_offsets, num_experts,
                                sf_rows_padded, silu_mul, codes, sf, stream, nullptr, 1);
+}
+
+extern "C" int b200fp4_experts_quantize_scatter(const void* x, int in_dtype, int64_t n_src, int64_t K, int64_t topk,
+                                                const int32_t* src2dst, const float* global_scales,
+                                                const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                                int32_t num_experts, int64_t sf_rows_padded, const int32_t* topk_ids,
+                                                const int32_t* expert_map, int64_t global_E, void* codes, void* sf,
+                                                void* stream) {
+  if (expert_map && (!topk_ids || global_E <= 0)) return B200FP4_STATUS_INVALID_VALUE;
+  if (n_src < 0 || K <= 0 || (K % 16) != 0 || topk <= 0 || num_experts <= 0 || sf_rows_padded < 0 ||
+      (sf_rows_padded % 128) != 0)
+    return B200FP4_STATUS_INVALID_VALUE;
+  if (in_dtype != B200FP4_DTYPE_F16 && in_dtype != B200FP4_DTYPE_BF16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (topk > kScatterMaxTopk || n_src > 0x7FFFFFFF) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (!global_scales || !expert_offsets || !blockscale_offsets || !sf) return B200FP4_STATUS_INVALID_VALUE;
+  if (n_src > 0 && (!x || !codes || !src2dst || !aligned(x, 16) || !aligned(codes, 4))) return B200FP4_STATUS_INVALID_VALUE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t KB = K / 16;
+  if (cudaMemsetAsync(sf, 0, (size_t)(sf_rows_padded * (((KB + 3) / 4) * 4)), st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  if (n_src == 0) return finish_launch(1);
+  if (in_dtype == B200FP4_DTYPE_BF16)
+    experts_quantize_scatter_kernel<__nv_bfloat16><<<(unsigned)n_src, kScatterThreads, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), K, (int)topk, src2dst, global_scales, expert_offsets, blockscale_offsets,
+        num_experts, topk_ids, expert_map, (int)global_E, (uint8_t*)codes, (uint8_t*)sf);
+  else
+    experts_quantize_scatter_kernel<__half><<<(unsigned)n_src, kScatterThreads, 0, st>>>(
+        reinterpret_cast<const __half*>(x), K, (int)topk, src2dst, global_scales, expert_offsets, blockscale_offsets,
+        num_experts, topk_ids, expert_map, (int)global_E, (uint8_t*)codes, (uint8_t*)sf);
+  return finish_launch(2);
 }
 
 extern "C" int b200fp4_experts_quantize_gather(const void* x, int in_dtype, int64_t M, int64_t K, const float* global_scales,

@@ -110,6 +110,41 @@ def shuffle_rows_scaled_fp4_experts_quant(input_tensor, dst2src_map, input_globa
     return codes, sf.view(torch.float8_e4m3fn)
 
 
+def scatter_scaled_fp4_experts_quant(input_tensor, output_permutation, topk, input_global_scale, expert_offsets,
+                                     blockscale_offsets, topk_ids=None, expert_map=None):
+    """The result of shuffle_rows_scaled_fp4_experts_quant computed token-major: row t of input_tensor [M, K] is
+    read once and quantized for each destination output_permutation[t*topk + s] (negative = none) with the global
+    scale of the expert that owns that row.  Rows no pair maps to are left unwritten.  topk <= 32.
+    topk_ids (int32 [M, topk], with expert_map if one was used) lets the kernel read the owning expert from the
+    routing instead of searching expert_offsets for it."""
+    dev = require_cuda(input_tensor, output_permutation, input_global_scale, expert_offsets, blockscale_offsets)
+    require(input_tensor.dim() == 2 and input_tensor.is_contiguous(), "input must be a contiguous 2-D tensor")
+    require(input_tensor.dtype in (torch.float16, torch.bfloat16), "input must be float16 or bfloat16")
+    require(output_permutation.dtype == torch.int32 and output_permutation.is_contiguous(), "map must be contiguous int32")
+    M, K = input_tensor.shape
+    rows = output_permutation.numel()
+    require(rows == M * topk and 0 < topk <= 32, "output_permutation must hold M*topk entries, topk <= 32")
+    require(K % 16 == 0, "K must be a multiple of 16")
+    E = expert_offsets.numel() - 1
+    require(input_global_scale.dtype == torch.float32 and input_global_scale.numel() >= E, "one f32 global scale per expert")
+    sf_rows = (rows + 127) // 128 * 128 + 128 * E
+    codes = torch.empty((rows, K // 2), dtype=torch.uint8, device=dev)
+    sf = torch.empty((sf_rows, (K // 16 + 3) // 4 * 4), dtype=torch.uint8, device=dev)
+    ids = emap = None
+    if topk_ids is not None:
+        ids = (topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)).contiguous()
+        require(ids.is_cuda and ids.numel() == rows, "topk_ids must be a CUDA tensor [M, topk]")
+        if expert_map is not None and expert_map.numel() > 0:
+            emap = expert_map.to(torch.int32).contiguous()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200fp4_experts_quantize_scatter(
+            ptr(input_tensor), dtype_code(input_tensor.dtype), M, K, topk, ptr(output_permutation), ptr(input_global_scale),
+            ptr(expert_offsets), ptr(blockscale_offsets), E, sf_rows, ptr(ids), ptr(emap),
+            0 if emap is None else emap.numel(), ptr(codes), ptr(sf), stream_ptr(dev)),
+            "scatter_scaled_fp4_experts_quant")
+    return codes, sf.view(torch.float8_e4m3fn)
+
+
 def silu_and_mul_scaled_fp4_experts_quant(input_tensor, input_global_scale, expert_offsets, blockscale_offsets, topk=None):
     """SiLU(x[:, :K]) * x[:, K:] then per-expert NVFP4 quantization."""
     return _experts_quant(input_tensor, input_global_scale, expert_offsets, blockscale_offsets, True)
@@ -190,7 +225,7 @@ def moe_unpermute_reduce(expert_out, output_permutation, topk_weights):
 def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs,
                       a1_gs, a2_gs, expert_map=None):
     """One MoE layer over dense NVFP4 expert weights (the flow of cutlass_moe.py:567-663):
-    permute metadata -> gather + quantize -> grouped GEMM (gate_up) with SiLU*up + quantize in its epilogue ->
+    permute metadata -> quantize each token for its experts -> grouped GEMM (gate_up) with SiLU*up + quantize in its epilogue ->
     grouped GEMM (down) -> combine.
 
     w13_codes [E,2I,H/2], w13_sf [E, swizzled(2I,H/16)], w13_gs [E] weight global scales (448*6/amax);
@@ -204,7 +239,10 @@ def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs,
     a_map = torch.empty(P, dtype=torch.int32, device=dev)
     c_map = torch.empty(P, dtype=torch.int32, device=dev)
     bso = get_cutlass_moe_mm_data(topk_ids, eo, None, None, a_map, c_map, E, N1 // 2, H, expert_map=expert_map)
-    xq, xsf = shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, a1_gs, eo, bso)
+    if topk <= 32:
+        xq, xsf = scatter_scaled_fp4_experts_quant(hidden, c_map, topk, a1_gs, eo, bso, topk_ids, expert_map)
+    else:
+        xq, xsf = shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, a1_gs, eo, bso)
     alpha1 = (1.0 / (a1_gs * w13_gs)).float()
     if N1 % 256 == 0:
         hq, hsf = cutlass_fp4_moe_mm_silu_and_mul_quant(xq, w13_codes, xsf, w13_sf, alpha1, eo, bso, a2_gs, hidden.dtype)

@@ -103,6 +103,21 @@ B200FP4_API int b200fp4_experts_quantize_gather(const void* x, int in_dtype, int
                                                 int64_t sf_rows_padded, const int32_t* row_map,
                                                 int32_t row_div, void* codes, void* sf, void* stream);
 
+/* The same result computed token-major: source row t (of n_src) is read once and quantized for each of
+ * its topk destination rows src2dst[t*topk + s] (the pair -> permuted row map of b200fp4_moe_permute;
+ * negative = the pair has no local destination), each with the global scale of the expert owning the
+ * destination row.  Destination rows that no pair maps to are not written.  topk <= 32.
+ * topk_ids [n_src, topk] (+ expert_map [global_E] or NULL), when given, must be the routing the map was
+ * built from: the owning expert is then read from it instead of searched for in expert_offsets. */
+B200FP4_API int b200fp4_experts_quantize_scatter(const void* x, int in_dtype, int64_t n_src, int64_t K,
+                                                 int64_t topk, const int32_t* src2dst,
+                                                 const float* global_scales,
+                                                 const int32_t* expert_offsets,
+                                                 const int32_t* blockscale_offsets, int32_t num_experts,
+                                                 int64_t sf_rows_padded, const int32_t* topk_ids,
+                                                 const int32_t* expert_map, int64_t global_E,
+                                                 void* codes, void* sf, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Part 2 -- dense block-scaled NVFP4 GEMM:  out[M,N] = alpha * (a . sfa)(b . sfb)^T.
  * Replaces cudaFP4GemmEx (declared, never defined) of cutlass_nvfp4/cuda_fp4_gemm.h:94-105 and the

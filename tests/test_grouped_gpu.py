@@ -247,3 +247,26 @@ def test_gather_quant_matches_shuffle_then_quant():
     c_new, s_new = gm.shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, gs, eo, bso)
     assert torch.equal(c_ref, c_new)
     assert torch.equal(s_ref.view(torch.uint8), s_new.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_scatter_quant_matches_gather_quant(dtype):
+    """Token-major quantization writes the bytes of the row-major gather for every permuted row, with an
+    expert_map that drops pairs (destinations < 0) and K larger than one pass of the block."""
+    from dgx_vllm_b200 import grouped_moe as gm
+    M, E_global, topk, K = 70, 12, 5, 4096 + 64
+    _, ids = _routing(M, E_global, topk, 21)
+    emap = np.full(E_global, -1, np.int32)
+    emap[[0, 2, 3, 7, 8, 11]] = np.arange(6)
+    E = 6
+    eo, bso, a_map, c_map = _metadata(ids, E, emap)
+    hidden = torch.randn(M, K, generator=torch.Generator().manual_seed(4)).to(dtype).cuda()
+    gs = torch.linspace(40.0, 300.0, E).cuda()
+    ref_q, ref_sf = gm.shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, gs, eo, bso)
+    rows = int(to_np(eo)[-1])
+    assert 0 < rows < M * topk
+    # with the owning expert searched for in expert_offsets, and read from the routing
+    for kw in ({}, {"topk_ids": ids.cuda(), "expert_map": torch.from_numpy(emap).cuda()}):
+        got_q, got_sf = gm.scatter_scaled_fp4_experts_quant(hidden, c_map, topk, gs, eo, bso, **kw)
+        np.testing.assert_array_equal(to_np(got_q)[:rows], to_np(ref_q)[:rows])
+        np.testing.assert_array_equal(to_np(got_sf), to_np(ref_sf))      # padding rows are zero in both
