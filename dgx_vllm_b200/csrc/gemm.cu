@@ -927,9 +927,14 @@ static int grouped_gemm_impl(const void* a_codes, const void* b_codes, const voi
   p.q_inter = fused ? (int)(N / 2) : 0;
   p.q_sf = reinterpret_cast<uint8_t*>(q_sf);
   p.q_gs = q_gs;
-  // short K means short main loops: prefer the double-buffered narrow tile there
+  // short K means short main loops: prefer the double-buffered narrow tile there, unless there are several
+  // waves of wide tiles anyway (then halving the A re-reads and the tile count wins: 171 vs 183 us on
+  // 81,920 rows x 2048 columns, K = 512)
   int bn = tile_n;
-  if (bn == 0) bn = (K >= 2048 && N % 256 == 0) ? 256 : 128;
+  if (bn == 0) {
+    const long long wide_tiles = (long long)max_tiles * (N / 256);
+    bn = (N % 256 == 0 && (K >= 2048 || wide_tiles >= 4LL * sm_count())) ? 256 : 128;
+  }
   if (fused) bn = 256;
   const int kb = stage_kblocks();
   CUtensorMap ma, mb;

@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kScatterThreads)
                                     const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
                                     int global_E, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
   __shared__ float s_gs[kScatterMaxTopk], s_rcp[kScatterMaxTopk];
-  __shared__ long long s_sfrow[kScatterMaxTopk];
+  __shared__ long long s_sfrow[kScatterMaxTopk], s_code[kScatterMaxTopk];
   __shared__ int s_dst[kScatterMaxTopk];
   const int64_t t = blockIdx.x;
   const int64_t CPR = K >> 3, KB = K >> 4, KT = (KB + 3) >> 2;
@@ -228,7 +228,9 @@ __global__ void __launch_bounds__(kScatterThreads)
     s_dst[threadIdx.x] = dst;
     s_gs[threadIdx.x] = gs;
     s_rcp[threadIdx.x] = __frcp_rn(gs + (gs == 0.f ? 1.0e8f : 0.f));
-    s_sfrow[threadIdx.x] = row;
+    // byte offsets of the destination row in the code tensor and of its first scale byte, computed once per block
+    s_sfrow[threadIdx.x] = sf_swizzled_offset(row, 0, KT);
+    s_code[threadIdx.x] = (long long)dst * (long long)(K >> 1);
   }
   __syncthreads();
   for (int64_t base = 0; base < CPR; base += kScatterThreads) {
@@ -244,6 +246,8 @@ __global__ void __launch_bounds__(kScatterThreads)
     float v[8];
     unpack8<T>(raw, v);
     const float sixth = __fmul_rn(amax, 0.16666667163372039794921875f);
+    const int64_t kb = kc >> 1;
+    const int64_t sf_col = (kb >> 2) * 512 + (kb & 3);     // scale byte of this block of 16 relative to its row's first
     for (int sl = 0; sl < topk; ++sl) {
       const int dst = s_dst[sl];
       if (dst < 0 || !ok) continue;
@@ -253,8 +257,8 @@ __global__ void __launch_bounds__(kScatterThreads)
       const uint32_t packed =
           f32x8_to_e2m1(__fmul_rn(v[0], os), __fmul_rn(v[1], os), __fmul_rn(v[2], os), __fmul_rn(v[3], os),
                         __fmul_rn(v[4], os), __fmul_rn(v[5], os), __fmul_rn(v[6], os), __fmul_rn(v[7], os));
-      *reinterpret_cast<uint32_t*>(codes + (int64_t)dst * (K >> 1) + kc * 4) = packed;
-      if ((kc & 1) == 0) sf[sf_swizzled_offset(s_sfrow[sl], kc >> 1, KT)] = sfb;
+      *reinterpret_cast<uint32_t*>(codes + s_code[sl] + kc * 4) = packed;
+      if ((kc & 1) == 0) sf[s_sfrow[sl] + sf_col] = sfb;
     }
   }
 }
