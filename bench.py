@@ -336,8 +336,9 @@ def bench_moe_prefill_ep(dev, flush, world: int, rank: int, steps: int = 5):
 
 def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     """BASELINE configs[3]: 8192 tokens x hidden 2048, 512 experts, Zipf(1.1)-skewed top-10 routing,
-    dense NVFP4 experts (gate_up 1024x2048, down 2048x512) through the grouped path: permute ->
-    per-expert quantize -> grouped GEMM -> SiLU*up + quantize -> grouped GEMM -> combine."""
+    dense NVFP4 experts (gate_up 1024x2048, down 2048x512) through the grouped path: routing metadata ->
+    token-major per-expert quantize -> grouped GEMM with SiLU*up + quantize in its epilogue -> grouped GEMM ->
+    un-permute + weighted sum."""
     import torch
     from dgx_vllm_b200 import grouped_moe as gm
     from dgx_vllm_b200 import scaled_fp4_quant, synth
@@ -352,9 +353,10 @@ def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     tw, ids = synth.make_routing(T, E, topk, 6, dev, zipf=1.1)
     a1 = (448.0 * 6.0 / hidden.float().abs().max()).repeat(E).float()
     a2 = torch.full((E,), 448.0 * 6.0 / 2.0, dtype=torch.float32, device=dev)
+    alphas = gm.nvfp4_moe_alphas(w13g, w2g, a1, a2)     # layer constants
 
     def run():
-        return gm.nvfp4_moe_prefill(hidden, tw, ids, w13c, w13s, w13g, w2c, w2s, w2g, a1, a2)
+        return gm.nvfp4_moe_prefill(hidden, tw, ids, w13c, w13s, w13g, w2c, w2s, w2g, a1, a2, alphas=alphas)
 
     for _ in range(3):
         run()
@@ -373,7 +375,7 @@ def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     wbytes = E * (2 * I * H + H * I) * 0.5625
     return {"tokens_per_s": T / t, "ms": t * 1e3, "tflops": flops / t / 1e12, "weight_GBps": wbytes / t / 1e9,
             "frac_of_measured_hbm_weights_only": wbytes / t / 1e9 / hbm_peak, "gemm_status": status,
-            "config": "8192 tokens, 512 experts, Zipf(1.1) top-10, dense NVFP4 experts, grouped path, 9 launches"}
+            "config": "8192 tokens, 512 experts, Zipf(1.1) top-10, dense NVFP4 experts, grouped path, 10 kernel launches"}
 
 
 def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_layers: int = 4, reps: int = 5):

@@ -14,10 +14,11 @@ from ._torch_util import dtype_code, ptr, require, require_cuda, stream_ptr, wor
 
 def get_cutlass_moe_mm_data(topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation,
                             output_permutation, num_experts, n, k, blockscale_offsets=None, is_gated=True,
-                            expert_map=None):
+                            expert_map=None, pair_indices: bool = False):
     """Fills, in place: expert_offsets [E+1], blockscale_offsets [E+1], problem_sizes1/2 [E,3],
     input_permutation [M*topk] (permuted row -> source token row, -1 past the end) and
-    output_permutation [M*topk] (pair -> permuted row, -1 if not local)."""
+    output_permutation [M*topk] (pair -> permuted row, -1 if not local).  pair_indices=True leaves
+    input_permutation holding pair indices (token*topk + slot) as the C routine writes them."""
     dev = require_cuda(topk_ids, expert_offsets, input_permutation, output_permutation)
     M, topk = topk_ids.shape
     ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
@@ -45,7 +46,8 @@ def get_cutlass_moe_mm_data(topk_ids, expert_offsets, problem_sizes1, problem_si
         problem_sizes2[:, 1] = k
         problem_sizes2[:, 2] = n
     # the C routine records pair indices; vLLM's a_map holds source token rows
-    torch.div(input_permutation, topk, rounding_mode="floor", out=input_permutation)
+    if not pair_indices:
+        torch.div(input_permutation, topk, rounding_mode="floor", out=input_permutation)
     return bso
 
 
@@ -222,8 +224,14 @@ def moe_unpermute_reduce(expert_out, output_permutation, topk_weights):
     return out
 
 
+def nvfp4_moe_alphas(w13_gs, w2_gs, a1_gs, a2_gs):
+    """The per-expert output scales of the two grouped GEMMs, 1 / (activation scale * weight scale): constants
+    of a layer, computed once and passed to nvfp4_moe_prefill as alphas=."""
+    return (1.0 / (a1_gs * w13_gs)).float().contiguous(), (1.0 / (a2_gs * w2_gs)).float().contiguous()
+
+
 def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs,
-                      a1_gs, a2_gs, expert_map=None):
+                      a1_gs, a2_gs, expert_map=None, alphas=None):
     """One MoE layer over dense NVFP4 expert weights (the flow of cutlass_moe.py:567-663):
     permute metadata -> quantize each token for its experts -> grouped GEMM (gate_up) with SiLU*up + quantize in its epilogue ->
     grouped GEMM (down) -> combine.
@@ -238,12 +246,13 @@ def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs,
     eo = torch.empty(E + 1, dtype=torch.int32, device=dev)
     a_map = torch.empty(P, dtype=torch.int32, device=dev)
     c_map = torch.empty(P, dtype=torch.int32, device=dev)
-    bso = get_cutlass_moe_mm_data(topk_ids, eo, None, None, a_map, c_map, E, N1 // 2, H, expert_map=expert_map)
+    alpha1, alpha2 = alphas if alphas is not None else nvfp4_moe_alphas(w13_gs, w2_gs, a1_gs, a2_gs)
+    bso = get_cutlass_moe_mm_data(topk_ids, eo, None, None, a_map, c_map, E, N1 // 2, H, expert_map=expert_map,
+                                  pair_indices=topk <= 32)
     if topk <= 32:
         xq, xsf = scatter_scaled_fp4_experts_quant(hidden, c_map, topk, a1_gs, eo, bso, topk_ids, expert_map)
     else:
         xq, xsf = shuffle_rows_scaled_fp4_experts_quant(hidden, a_map, a1_gs, eo, bso)
-    alpha1 = (1.0 / (a1_gs * w13_gs)).float()
     if N1 % 256 == 0:
         hq, hsf = cutlass_fp4_moe_mm_silu_and_mul_quant(xq, w13_codes, xsf, w13_sf, alpha1, eo, bso, a2_gs, hidden.dtype)
     else:
@@ -251,5 +260,5 @@ def nvfp4_moe_prefill(hidden, topk_weights, topk_ids, w13_codes, w13_sf, w13_gs,
         cutlass_fp4_moe_mm(c1, xq, w13_codes, xsf, w13_sf, alpha1, None, eo, bso)
         hq, hsf = silu_and_mul_scaled_fp4_experts_quant(c1, a2_gs, eo, bso)
     c2 = torch.empty((P, H), dtype=hidden.dtype, device=dev)
-    cutlass_fp4_moe_mm(c2, hq, w2_codes, hsf, w2_sf, (1.0 / (a2_gs * w2_gs)).float(), None, eo, bso)
+    cutlass_fp4_moe_mm(c2, hq, w2_codes, hsf, w2_sf, alpha2, None, eo, bso)
     return moe_unpermute_reduce(c2, c_map, topk_weights)
