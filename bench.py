@@ -481,10 +481,21 @@ def main():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parts", action="store_true", help="skip the dense GEMM / quantizer side measurements")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="run just the grouped prefill layer (the `moe_prefill_8192_tokens` part) and print its numbers; "
+                         "a short command for profiling that path")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
+    if args.only_prefill:
+        import torch
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        hbm_peak, _ = measured_peaks()
+        print(json.dumps({"moe_prefill_8192_tokens": bench_moe_prefill(dev, flush, hbm_peak)}))
+        return 0
 
     import torch
     import torch.distributed as dist
