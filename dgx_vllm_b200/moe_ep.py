@@ -195,12 +195,16 @@ class ExpertParallelMoEPrefill:
         self.weights = weights       # (w13_codes, w13_sf, w13_gs, w2_codes, w2_sf, w2_gs, a1_gs, a2_gs) of the local experts
         self._fn = local_fn
         self._emap = None
+        self._alphas = None
 
     def _local(self, hidden, topk_w, topk_ids, emap):
         if self._fn is not None:
             return self._fn(hidden, topk_w, topk_ids, emap)
-        from .grouped_moe import nvfp4_moe_prefill
-        return nvfp4_moe_prefill(hidden, topk_w, topk_ids, *self.weights, expert_map=emap)
+        from .grouped_moe import nvfp4_moe_alphas, nvfp4_moe_prefill
+        if self._alphas is None:     # layer constants
+            w = self.weights
+            self._alphas = nvfp4_moe_alphas(w[2], w[5], w[6], w[7])
+        return nvfp4_moe_prefill(hidden, topk_w, topk_ids, *self.weights, expert_map=emap, alphas=self._alphas)
 
     def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         if self._emap is None or self._emap.device != hidden.device:
