@@ -469,6 +469,9 @@ __global__ void __launch_bounds__(1024)
   __shared__ int s_base;
   const int tid = threadIdx.x;
   if (tid == 0) s_base = 0;
+  // the four ints in front of hdr are the GEMM's status word (0 = ok) and its padding: cleared here with hdr, so the
+  // call needs no separate memset
+  if (tid < 8) hdr[tid - 4] = 0;
   __syncthreads();
   for (int e0 = 0; e0 < E; e0 += 1024) {
     const int e = e0 + tid;
@@ -941,15 +944,11 @@ static int grouped_gemm_impl(const void* a_codes, const void* b_codes, const voi
   if (!make_map(&ma, a_codes, (uint64_t)rows_capacity, (uint64_t)K / 2, kBM, kb * 32) ||
       !make_map(&mb, b_codes, (uint64_t)(E * N), (uint64_t)K / 2, fused ? 128u : (uint32_t)bn, kb * 32))
     return B200FP4_STATUS_INTERNAL_ERROR;
-  if (cudaMemsetAsync(workspace, 0, 32, st) != cudaSuccess) {
-    cudaGetLastError();
-    return B200FP4_STATUS_EXECUTION_FAILED;
-  }
   grouped_tiles_kernel<<<1, 1024, 0, st>>>(expert_offsets, sf_offsets, (int)E, const_cast<int*>(p.g_hdr),
                                            const_cast<int4*>(p.g_mtiles), max_tiles);
   int rc = fused ? launch_gemm<256, 4, true, true>(ma, mb, p, max_tiles, st) : dispatch_gemm<true>(bn, kb, ma, mb, p, max_tiles, st);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
-  return finish_launch(3);
+  return finish_launch(2);
 }
 
 extern "C" int b200fp4_grouped_gemm_nvfp4(const void* a_codes, const void* b_codes, const void* a_sf, const void* b_sf,
