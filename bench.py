@@ -31,6 +31,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+sys.path.insert(1, os.path.join(ROOT, "tests"))     # synthetic-data generators shared with the tests
 
 E_TOTAL, HIDDEN, INTER, TOPK = 512, 2048, 512, 10
 BYTES_PER_EXPERT_GATE_UP = 2 * INTER * HIDDEN * 7 // 16          # comp 1/4 + meta 1/8 + scale 1/16 B per weight
@@ -106,7 +107,8 @@ class ClockSampler:
 
 def build_case(dev, e_local: int, batch: int, rank: int):
     import torch
-    from dgx_vllm_b200 import scaled_fp4_quant, synth
+    import synth
+    from dgx_vllm_b200 import scaled_fp4_quant
 
     def qfn(w, gs):
         c, s = scaled_fp4_quant(w, gs, is_sf_swizzled_layout=False)
@@ -127,7 +129,7 @@ def cpu_baseline(batch: int, max_seconds: float = 25.0):
     The sample is one batch routed over a reduced expert table (same per-expert shapes), repeated
     until ~max_seconds of CPU work have been spent."""
     import torch
-    from dgx_vllm_b200 import synth
+    import synth
     from oracle import emulation
     import oracle
     import numpy as np
@@ -183,7 +185,8 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
     N=14336, K=4096, M in {128,1024,4096}, activation quantized on the fly) and the quantizer alone.
     Each iteration is timed on its own with CUDA events after rewriting a 256 MiB buffer (cold L2)."""
     import torch
-    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant, synth
+    import synth
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant
 
     def timed(fn, n):
         ts = []
@@ -242,7 +245,7 @@ def bench_dense_nshard(dev, flush, world: int, rank: int, steps: int = 10):
     after an L2 flush), max over ranks."""
     import torch
     import torch.distributed as dist
-    from dgx_vllm_b200 import synth
+    import synth
     from dgx_vllm_b200.dense_shard import ColumnShardedNvfp4Linear, shard_rows
 
     N, K = 14336, 4096
@@ -283,7 +286,8 @@ def bench_dense_nshard(dev, flush, world: int, rank: int, steps: int = 10):
 def _dense_experts(dev, gen, E, N, K):
     """E dense NVFP4 expert matrices [N,K]: (codes [E,N,K/2], swizzled scales, global scales [E])."""
     import torch
-    from dgx_vllm_b200 import scaled_fp4_quant, synth
+    import synth
+    from dgx_vllm_b200 import scaled_fp4_quant
     codes = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
     sf = torch.empty(E, (N + 127) // 128 * 128, (K // 16 + 3) // 4 * 4, dtype=torch.uint8, device=dev)
     gs = torch.empty(E, dtype=torch.float32, device=dev)
@@ -303,7 +307,7 @@ def bench_moe_prefill_ep(dev, flush, world: int, rank: int, steps: int = 5):
     the fp32 partial rows.  Device time per layer, max over ranks."""
     import torch
     import torch.distributed as dist
-    from dgx_vllm_b200 import synth
+    import synth
     from dgx_vllm_b200.moe_ep import ExpertParallelMoEPrefill
 
     T, E, H, I, topk = 8192, 512, 2048, 512, 10
@@ -341,7 +345,8 @@ def bench_moe_prefill(dev, flush, hbm_peak, steps: int = 5):
     un-permute + weighted sum."""
     import torch
     from dgx_vllm_b200 import grouped_moe as gm
-    from dgx_vllm_b200 import scaled_fp4_quant, synth
+    import synth
+    from dgx_vllm_b200 import scaled_fp4_quant
     from dgx_vllm_b200.ops import last_gemm_status
 
     T, E, H, I, topk = 8192, 512, 2048, 512, 10
@@ -385,7 +390,8 @@ def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_lay
     Weights: `distinct_layers` independent layer sets cycled over the 48 layers (each set is 704 MB of
     routed weights, far beyond L2, and every layer uses its own routing)."""
     import torch
-    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant, synth
+    import synth
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant
     from dgx_vllm_b200 import grouped_moe as gm
     from dgx_vllm_b200 import sparse_fp4_v7 as sp7
 

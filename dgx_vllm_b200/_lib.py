@@ -55,6 +55,21 @@ SIGNATURES = {
     "b200fp4_fused_moe_profile_events": (None, [_vp, _vp, _vp]),
     "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                         _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_fused_moe_set_wait_limit": (None, [_i64, _i32]),
+    "b200fp4_fused_moe_last_status": (_i32, [_vp, _vp, _vp]),
+    # the reference's declared C API (cutlass_nvfp4/cuda_fp4_gemm.h) under its own names
+    "cudaFP4Create": (_i32, [_vp]),
+    "cudaFP4Destroy": (_i32, [_vp]),
+    "cudaFP4SetStream": (_i32, [_vp, _vp]),
+    "cudaFP4GemmEx": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, ctypes.c_float, _vp, _vp, ctypes.c_float, _vp, _i32]),
+    "cudaFP4Gemm": (_i32, [_vp, _i32, _i32, _i32, ctypes.c_float, _vp, _vp, _vp]),
+    "cudaFP4GetVersionString": (ctypes.c_char_p, []),
+    "cudaFP4GetVersion": (_i32, []),
+    "cudaFP4HasHardwareAcceleration": (_i32, []),
+    "cudaFP4GetErrorString": (ctypes.c_char_p, [_i32]),
+    "cudaFP4ConvertFromFP32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "cudaFP4ConvertToFP32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "cudaFP4Quantize": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "b200fp4_fused_moe_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "b200fp4_fused_sparse_moe_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                              _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),

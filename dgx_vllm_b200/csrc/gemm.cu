@@ -25,16 +25,6 @@
 
 namespace b200fp4 {
 
-// CTA-pair (cta_group::2) kernel, gemm2.cu
-int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
-                     void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
-// gemm4.cu: 128 x 192 tiles, two accumulators (epilogue overlapped with the next tile)
-int launch_gemm_overlap(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
-                        void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
-// gemm3.cu: 256 x 224 tiles (two 128-row halves of A per CTA)
-int launch_gemm_tall(const CUtensorMap& ma, const CUtensorMap& mb, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
-                     void* out, int out_bf16, int M, int N, int K, int* status, cudaStream_t st);
-
 namespace {
 
 constexpr int kBM = 128;
@@ -47,6 +37,7 @@ struct GemmParams {
   const float* alpha;
   void* out;
   int out_bf16;
+  int out_f32;          // dense mode only: out is fp32 [M, N] (the accumulator times alpha, unrounded)
   int M, N, K;
   int m_tiles, n_tiles, k_stages;
   int* status;          // 0 = ok; otherwise the code of the wait that expired
@@ -390,6 +381,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           *reinterpret_cast<uint32_t*>(p.q_sf + ((size_t)ti.sfa_tile * kt2 + (size_t)(ti.n0 / 64 + half)) * 512 + lane * 16 +
                                        quarter * 4) = sf4;
         }
+        continue;
+      }
+      if (!kGrouped && p.out_f32) {
+        // fp32 output (the cudaFP4GemmEx form): each 32-column chunk goes straight from tensor memory to global
+        // memory; the accumulator is handed back after the last chunk
+        float* dst_row = reinterpret_cast<float*>(p.out) + (size_t)row * p.N;
+#pragma unroll 1
+        for (int c = 0; c < CH; ++c) {
+          uint32_t r[32];
+          tcgen05_ld_32x32(taddr + (c_first + c) * 32, r);
+          tcgen05_wait_ld();
+          const int col0 = ti.n0 + (c_first + c) * 32;
+          if (row < ti.row_end && col0 < p.N) {
+            if (col0 + 32 <= p.N && (p.N % 4) == 0) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(dst_row + col0)[i] =
+                    make_float4(__uint_as_float(r[4 * i]) * alpha, __uint_as_float(r[4 * i + 1]) * alpha,
+                                __uint_as_float(r[4 * i + 2]) * alpha, __uint_as_float(r[4 * i + 3]) * alpha);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) dst_row[col0 + i] = __uint_as_float(r[i]) * alpha;
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
         continue;
       }
       // drain this thread's row of the accumulator into packed 16-bit registers ...
@@ -812,14 +832,15 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
                                   const float* alpha, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
                                   int tile_n, void* workspace, size_t workspace_bytes, void* stream) {
   if (M < 0 || N <= 0 || K <= 0 || (K % 64) != 0) return B200FP4_STATUS_INVALID_VALUE;
-  if (out_dtype != B200FP4_DTYPE_BF16 && out_dtype != B200FP4_DTYPE_F16) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (out_dtype != B200FP4_DTYPE_BF16 && out_dtype != B200FP4_DTYPE_F16 && out_dtype != B200FP4_DTYPE_F32)
+    return B200FP4_STATUS_NOT_SUPPORTED;
   if (M == 0) return B200FP4_STATUS_SUCCESS;
   if (!a_codes || !b_codes || !sfa || !sfb || !alpha || !out) return B200FP4_STATUS_INVALID_VALUE;
   if (!aligned(a_codes, 16) || !aligned(b_codes, 16) || !aligned(sfa, 16) || !aligned(sfb, 16) || !aligned(out, 16) ||
       ((K / 2) % 16) != 0)
     return B200FP4_STATUS_INVALID_VALUE;
   if (!workspace || workspace_bytes < 256 || !aligned(workspace, 16)) return B200FP4_STATUS_ALLOC_FAILED;
-  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 224 && tile_n != 192 && tile_n != 512) return B200FP4_STATUS_INVALID_VALUE;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return B200FP4_STATUS_INVALID_VALUE;
   if (M > (1 << 24) || N > (1 << 24) || K > (1 << 24)) return B200FP4_STATUS_NOT_SUPPORTED;
   if (b200fp4_has_hardware_acceleration() != 1) return B200FP4_STATUS_ARCH_MISMATCH;
   cudaStream_t st = (cudaStream_t)stream;
@@ -829,6 +850,7 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   p.alpha = alpha;
   p.out = out;
   p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
+  p.out_f32 = out_dtype == B200FP4_DTYPE_F32;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.m_tiles = (int)((M + kBM - 1) / kBM);
   p.status = reinterpret_cast<int*>(workspace);
@@ -840,34 +862,6 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   if (cudaMemsetAsync(workspace, 0, 16, st) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
-  }
-  if (bn == 192) {
-    CUtensorMap pa, pb;
-    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 128, 128) ||
-        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 192, 128))
-      return B200FP4_STATUS_INTERNAL_ERROR;
-    int rc4 = launch_gemm_overlap(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
-    if (rc4 != B200FP4_STATUS_SUCCESS) return rc4;
-    return finish_launch(2);
-  }
-  if (bn == 224) {
-    CUtensorMap pa, pb;
-    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 256, 128) ||
-        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 224, 128))
-      return B200FP4_STATUS_INTERNAL_ERROR;
-    int rc3 = launch_gemm_tall(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
-    if (rc3 != B200FP4_STATUS_SUCCESS) return rc3;
-    return finish_launch(2);
-  }
-  if (bn == 512) {
-    // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2)
-    CUtensorMap pa, pb;
-    if (!make_map(&pa, a_codes, (uint64_t)M, (uint64_t)K / 2, 128, 128) ||
-        !make_map(&pb, b_codes, (uint64_t)N, (uint64_t)K / 2, 128, 128))
-      return B200FP4_STATUS_INTERNAL_ERROR;
-    int rc2 = launch_gemm_pair(pa, pb, p.sfa, p.sfb, alpha, out, p.out_bf16, (int)M, (int)N, (int)K, p.status, st);
-    if (rc2 != B200FP4_STATUS_SUCCESS) return rc2;
-    return finish_launch(2);
   }
   CUtensorMap ma, mb;
   if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM, kb * 32) ||
@@ -920,6 +914,7 @@ static int grouped_gemm_impl(const void* a_codes, const void* b_codes, const voi
   p.alpha = nullptr;
   p.out = out;
   p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
+  p.out_f32 = 0;
   p.M = (int)rows_capacity; p.N = (int)N; p.K = (int)K;
   p.m_tiles = max_tiles;
   p.status = reinterpret_cast<int*>(workspace);

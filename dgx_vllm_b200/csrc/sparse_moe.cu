@@ -70,6 +70,7 @@ struct GemvArgs {
   int N, K;
   int n_slabs;
   int inter;        // SiLU mode: gate columns [0, inter), up columns [inter, 2*inter)
+  long long wait_cycles;   // one-launch layer: clock64 budget of a wait on a pass counter
 };
 
 // ------------------------------------------------------------------------------------------ plan
@@ -768,13 +769,19 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(done + pass) : "memory");
     return v;
   };
+  // A wait that runs out of its clock budget records B200FP4_MOE_STATUS_WAIT_EXPIRED in the plan header (the layer's
+  // status word) and carries on with whatever the activation buffer holds; once the word is set no later wait of the
+  // launch polls at all, so a broken launch still ends promptly.
   auto wait_pass = [&](int pass, int seen) {
     if (kDep == 2 && tid == 0 && pass >= 0 && seen < need) {
-      const long long t0 = clock64();
-      while (load_count(pass) < need) {
-        if (clock64() - t0 > 2000000000LL) {   // ~1 s: give up, flag it, carry on (results of this pass are then wrong)
-          g.plan.hdr[3] = -1;
-          break;
+      volatile int* status = g.plan.hdr + 3;
+      if (*status == 0) {
+        const long long t0 = clock64();
+        while (load_count(pass) < need) {
+          if (clock64() - t0 > g.wait_cycles) {
+            *status = B200FP4_MOE_STATUS_WAIT_EXPIRED;
+            break;
+          }
         }
       }
     }
@@ -1051,6 +1058,12 @@ __global__ void weighted_reduce_kernel(const float* __restrict__ down, const flo
 // Optional CUDA events recorded around the two GEMV launches of the fused layer (benchmark hook).
 cudaEvent_t g_prof_events[3] = {nullptr, nullptr, nullptr};
 
+// One-launch layer: clock64 budget of a wait on a pass counter (~1 s at 2 GHz) and a diagnostic surplus added to the
+// count a down-projection item waits for (b200fp4_fused_moe_set_wait_limit).
+constexpr long long kDefaultWaitCycles = 2000000000LL;
+long long g_wait_cycles = kDefaultWaitCycles;
+int g_wait_extra_need = 0;
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int64_t max_passes(int64_t P, int64_t E) { return (P < E ? P : E) + P / kMaxTok + 1; }
@@ -1274,6 +1287,7 @@ GemvArgs make_args(const SparseWeights& w, const Plan& plan, const __half* A, in
   g.K = (int)K;
   g.inter = inter_silu;
   g.n_slabs = 1;
+  g.wait_cycles = g_wait_cycles;
   return g;
 }
 
@@ -1300,7 +1314,7 @@ int launch_fused_pair(GemvArgs ga, GemvArgs gb, int* done, int64_t P, int64_t E,
   if (state[dev] < 0) return B200FP4_STATUS_NOT_SUPPORTED;
   ga.n_slabs = ga.inter / (64 * CGA);
   gb.n_slabs = gb.N / (128 * CGB);
-  int need = ga.n_slabs;
+  int need = ga.n_slabs + g_wait_extra_need;
   const int64_t slabs = ga.n_slabs > gb.n_slabs ? ga.n_slabs : gb.n_slabs;
   int64_t grid = max_passes(P, E) * slabs;
   if (grid > (int64_t)sm_count()) grid = sm_count();
@@ -1507,6 +1521,23 @@ extern "C" void b200fp4_fused_moe_profile_events(void* before_gate_up, void* aft
   g_prof_events[2] = (cudaEvent_t)after_down;
 }
 
+extern "C" void b200fp4_fused_moe_set_wait_limit(int64_t cycles, int extra_need) {
+  g_wait_cycles = cycles > 0 ? (long long)cycles : kDefaultWaitCycles;
+  g_wait_extra_need = extra_need > 0 ? extra_need : 0;
+}
+
+extern "C" int b200fp4_fused_moe_last_status(const void* workspace, void* stream, int* status) {
+  if (!workspace || !status) return B200FP4_STATUS_INVALID_VALUE;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the status word is hdr[3] of the plan at the start of the layer's workspace
+  if (cudaMemcpyAsync(status, reinterpret_cast<const int*>(workspace) + 3, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  return B200FP4_STATUS_SUCCESS;
+}
+
 extern "C" size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I, int64_t E) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
   const int64_t P = M * topk;
@@ -1671,12 +1702,15 @@ extern "C" int b200fp4_fused_sparse_moe_host(const void* hidden_host, int h_dtyp
                                 w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, d_out, out_dtype, M, topk, H, I,
                                 E, flags, static_cast<char*>(workspace) + stage, workspace_bytes - stage, stream);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  int moe_status = 0;   // the layer's status word (hdr[3] of its plan) comes back with the result
   if (cudaMemcpyAsync(out_host, d_out, nh, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaMemcpyAsync(&moe_status, reinterpret_cast<const int*>(static_cast<char*>(workspace) + stage) + 3, sizeof(int),
+                      cudaMemcpyDeviceToHost, st) != cudaSuccess ||
       cudaStreamSynchronize(st) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
   }
-  return B200FP4_STATUS_SUCCESS;
+  return moe_status == 0 ? B200FP4_STATUS_SUCCESS : B200FP4_STATUS_INTERNAL_ERROR;
 }
 
 // ------------------------------------------------------------------------------------------ expert parallel

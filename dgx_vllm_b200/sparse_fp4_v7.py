@@ -217,6 +217,19 @@ def fused_sparse_moe_v7(hidden_states, topk_weights, topk_ids, expert_map,
     return out
 
 
+def last_moe_status(device=None) -> int:
+    """Status word of the most recent fused MoE layer issued through these mirrors on the current stream of
+    `device`: 0, or -1 when a bounded wait of the one-launch layer ran out (the result of that call is then not
+    valid).  Synchronises the stream (b200fp4_fused_moe_last_status)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    import ctypes
+    ws = workspace(dev, 256)
+    st = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200fp4_fused_moe_last_status(ptr(ws), stream_ptr(dev), ctypes.addressof(st)), "last_moe_status")
+    return int(st.value)
+
+
 class FusedSparseMoE:
     """`fused_sparse_moe_v7` with the weight arguments bound once.
 

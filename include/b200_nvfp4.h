@@ -130,13 +130,8 @@ B200FP4_API int b200fp4_experts_quantize_scatter(const void* x, int in_dtype, in
  *   sfa, sfb  E4M3 block scales in the padded 128x4-tile swizzled layout
  *             (b200fp4_sf_swizzled_bytes(rows, K/16) bytes each)
  *   alpha     device pointer to one f32 (= 1 / (global_scale_a * global_scale_b))
- *   out       [M, N] bf16 or f16
- *   tile_n    0 = choose; 128 or 256 forces the CTA tile width of the 128-row kernel; 192 selects the
- *             128 x 192 kernel with two accumulators (epilogue overlapped with the next tile); 224 the
- *             256 x 224 kernel (two 128-row halves of A per CTA); 512 selects the two-CTA kernel
- *             (a cluster of two SMs shares one 256x256 tile through tcgen05 cta_group::2) -- an
- *             opt-in variant that is never chosen automatically: it measured slower than the
- *             256-wide single-CTA kernel (260 us against 150 us at M=4096, N=14336, K=4096)
+ *   out       [M, N] bf16, f16 or f32 (f32: the accumulator times alpha, unrounded)
+ *   tile_n    0 = choose; 128 or 256 forces the CTA tile width (128 x tile_n output tiles)
  *   workspace b200fp4_gemm_workspace_bytes() bytes; its first int is a status word the kernel
  *             leaves at 0 unless one of its bounded barrier waits expired (then nothing it wrote
  *             may be trusted): read it after synchronising when diagnosing.
@@ -244,7 +239,22 @@ B200FP4_API int b200fp4_convert_to_sparse_2of4(const uint8_t* codes, const uint8
  * B200FP4_SPARSE_META_ORDERED as described above, for both weight sets.  With ordered metadata, the
  * usual shapes and up to 256 (token, expert) pairs both projections run in ONE cooperative launch
  * (blocks that finish their share of gate_up move on to the down projection of passes that are
- * already complete); B200FP4_MOE_SEPARATE_LAUNCHES keeps one launch per projection. */
+ * already complete); B200FP4_MOE_SEPARATE_LAUNCHES keeps one launch per projection.
+ *
+ * Status word.  In the one-launch form a down-projection item waits (bounded, ~1 s of SM clocks by default)
+ * for the gate_up items of its pass.  A wait that runs out writes B200FP4_MOE_STATUS_WAIT_EXPIRED to the
+ * layer's status word -- the fourth int of `workspace` -- skips every later wait of the launch and lets the
+ * kernel finish; the output of that call is then not to be trusted.  Every call clears the word first.
+ * b200fp4_fused_moe_last_status copies it to *status after synchronising `stream` (the one function of this
+ * library, with the *_host entry, that synchronises); the host-buffer entry checks it itself and returns
+ * B200FP4_STATUS_INTERNAL_ERROR.  b200fp4_fused_moe_set_wait_limit(cycles, extra_need) sets the clock64 budget
+ * of such a wait for later calls (cycles <= 0 restores the default) and, for diagnosis, adds `extra_need` to the
+ * number of finished gate_up items a wait asks for (0 in normal use; 1 makes every wait run out, which is how
+ * the time-out path is tested).  Process-global, not thread-safe.  No counterpart in the reference, whose
+ * kernels never wait on one another. */
+#define B200FP4_MOE_STATUS_WAIT_EXPIRED (-1)
+B200FP4_API void b200fp4_fused_moe_set_wait_limit(int64_t cycles, int extra_need);
+B200FP4_API int b200fp4_fused_moe_last_status(const void* workspace, void* stream, int* status);
 B200FP4_API size_t b200fp4_fused_moe_workspace_bytes(int64_t M, int64_t topk, int64_t H, int64_t I,
                                                      int64_t E);
 B200FP4_API int b200fp4_fused_sparse_moe(
@@ -353,6 +363,45 @@ B200FP4_API int b200fp4_fused_sparse_moe_records(
     int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream);
 B200FP4_API int b200fp4_ep_combine(const void* parts, int dtype, int64_t B, int64_t H, int64_t G,
                                    void* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The reference's declared C API, exported under its own names so that a program written against
+ * cutlass_nvfp4/cuda_fp4_gemm.h links against this library unchanged (the reference declares these
+ * functions and defines none of them).  Prototypes follow cuda_fp4_gemm.h:48-63 (handle), :94-105
+ * (cudaFP4GemmEx), :113-120 (cudaFP4Gemm), :124-147 (utilities), :161-203 (conversions); the
+ * reference's one-byte structs cuda_fp4x2_t / __nv_fp8_e4m3 appear as void pointers and cudaStream_t
+ * as void*, which is the same C ABI.  Skipped when the reference's header was included first.
+ *
+ *   cudaFP4GemmEx   C[M,N] f32 = (A . A_scales)(B . B_scales)^T * A_scale_global * B_scale_global with
+ *                   A [M,K/2], B [N,K/2] packed E2M1 and LINEAR E4M3 scales [M,K/16], [N,K/16];
+ *                   group_size must be 16 and K a multiple of 64.  Runs on the handle's stream.
+ *   cudaFP4Gemm     the same without block scales: C = alpha * A B^T.
+ *   cudaFP4Quantize fp32 [rows, cols] -> codes, linear E4M3 scales and *dst_scale_global (HOST
+ *                   pointer) = amax / (6 * 448); synchronises `stream` to return that scalar.
+ *   cudaFP4ConvertFromFP32 / ToFP32   element-wise E2M1 rounding (RNE, saturating) and decoding.
+ * E2M1 values are the NVFP4 set {0, .5, 1, 1.5, 2, 3, 4, 6}, not the reference header kernels'
+ * non-standard table (cutlass_nvfp4/nvfp4_types.cuh:56-64).  The handle keeps device scratch sized
+ * at cudaFP4Create for problems up to 8192^3 and grows it with cudaMalloc when a call needs more.
+ * ------------------------------------------------------------------------------------------- */
+#ifndef __CUDA_FP4_GEMM_H__
+typedef struct cudaFP4Handle_st* cudaFP4Handle_t;
+B200FP4_API int cudaFP4Create(cudaFP4Handle_t* handle);
+B200FP4_API int cudaFP4Destroy(cudaFP4Handle_t handle);
+B200FP4_API int cudaFP4SetStream(cudaFP4Handle_t handle, void* stream);
+B200FP4_API int cudaFP4GemmEx(cudaFP4Handle_t handle, int M, int N, int K, const void* A, const void* A_scales,
+                              float A_scale_global, const void* B, const void* B_scales, float B_scale_global,
+                              float* C, int group_size);
+B200FP4_API int cudaFP4Gemm(cudaFP4Handle_t handle, int M, int N, int K, float alpha, const void* A, const void* B,
+                            float* C);
+B200FP4_API const char* cudaFP4GetVersionString(void);
+B200FP4_API int cudaFP4GetVersion(void);
+B200FP4_API int cudaFP4HasHardwareAcceleration(void);
+B200FP4_API const char* cudaFP4GetErrorString(int status);
+B200FP4_API int cudaFP4ConvertFromFP32(void* dst, const float* src, int rows, int cols, void* stream);
+B200FP4_API int cudaFP4ConvertToFP32(float* dst, const void* src, int rows, int cols, void* stream);
+B200FP4_API int cudaFP4Quantize(void* dst_data, void* dst_scales, float* dst_scale_global, const float* src, int rows,
+                                int cols, int group_size, void* stream);
+#endif
 
 /* Benchmark hook (no counterpart in the reference): when the three cudaEvent_t handles are non-NULL,
  * b200fp4_fused_sparse_moe records them on its stream before the gate_up GEMV, between the two

@@ -306,6 +306,33 @@ def fused_sparse_moe(hidden, topk_w, topk_ids, expert_map, w13, w2, inter: int,
     return (down.astype(np.float64) * w).sum(1).astype(np.float32)
 
 
+def fused_sparse_moe_by_expert(hidden, topk_w, mapped_ids, fetch, inter: int,
+                               apply_router_weight_on_input: bool = False) -> np.ndarray:
+    """fused_sparse_moe(round_fp16=False) evaluated expert by expert, for layers whose expert table is too
+    large to expand on the host at once (512 experts): only the experts that `mapped_ids` names are
+    touched.  mapped_ids [M, topk] holds local expert ids, negative = the pair contributes nothing (what
+    expert_map does in fused_sparse_moe_v7, sparse_fp4_v7.cu:640-645).  fetch(e) returns
+    ((comp_T, meta_T, scale_T, g_scale), (comp_T, meta_T, scale_T, g_scale)) of expert e for the gate_up and
+    the down projection: 2-D arrays and one float each.  Same arithmetic as fused_sparse_moe: per pair
+    gate_up GEMV -> SiLU(gate)*up -> down GEMV in fp64 on the fp32 expansion, router-weighted sum per token."""
+    hidden = _c(hidden, np.float32)
+    ids = np.asarray(mapped_ids).astype(np.int64)
+    M, topk = ids.shape
+    w = _c(topk_w, np.float32).reshape(M, topk)
+    out = np.zeros((M, hidden.shape[1]), np.float64)
+    for e in np.unique(ids[ids >= 0]):
+        (c13, m13, s13, g13), (c2, m2, s2, g2) = fetch(int(e))
+        tok, slot = np.nonzero(ids == e)
+        W13 = sparse_expand(c13, m13, s13, g13).astype(np.float64)
+        gu = (hidden[tok].astype(np.float64) @ W13.T).astype(np.float32)
+        act = silu_mul(gu, inter)
+        W2 = sparse_expand(c2, m2, s2, g2).astype(np.float64)
+        down = (act.astype(np.float64) @ W2.T).astype(np.float32).astype(np.float64)
+        scale = np.ones(len(tok)) if apply_router_weight_on_input else w[tok, slot].astype(np.float64)
+        np.add.at(out, tok, down * scale[:, None])
+    return out.astype(np.float32)
+
+
 # ----------------------------------------------------------------------------- grouped GEMM
 
 def grouped_nvfp4_gemm(a_codes, a_sf, b_codes, b_sf, alphas, expert_offsets, problem_m) -> np.ndarray:

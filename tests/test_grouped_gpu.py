@@ -14,7 +14,7 @@ TOL = 1e-2
 
 
 def _routing(M, E, topk, seed, zipf=1.1):
-    from dgx_vllm_b200 import synth
+    import synth
     return synth.make_routing(M, E, topk, seed, "cpu", zipf=zipf)
 
 

@@ -19,7 +19,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_library_exports_every_declared_symbol():
     from dgx_vllm_b200 import _lib
     hdr = open(os.path.join(ROOT, "include", "b200_nvfp4.h")).read()
-    declared = set(re.findall(r"\b(b200fp4_[a-z0-9_]+)\s*\(", hdr))
+    declared = set(re.findall(r"\b(b200fp4_[a-z0-9_]+|cudaFP4[A-Za-z0-9]+)\s*\(", hdr))
     assert declared, "no declarations found"
     L = _lib.lib()
     for name in declared:
@@ -51,7 +51,7 @@ def test_product_does_not_import_oracle():
 
 
 def test_synth_sparse_experts_are_2of4_and_consistent():
-    from dgx_vllm_b200 import synth
+    import synth
     w = synth.make_sparse_experts(2, 32, 64, 0, "cpu", oracle_quantize_fn)
     assert tuple(w["comp_T"].shape) == (2, 16, 32) and tuple(w["meta_T"].shape) == (2, 8, 32)
     meta = w["meta_T"].numpy()
@@ -63,7 +63,7 @@ def test_synth_sparse_experts_are_2of4_and_consistent():
 
 
 def test_routing_generators():
-    from dgx_vllm_b200 import synth
+    import synth
     w, ids = synth.make_routing(16, 64, 10, 0, "cpu")
     assert ids.dtype == torch.int32 and w.dtype == torch.float32
     assert torch.allclose(w.sum(-1), torch.ones(16), atol=1e-5)
@@ -92,7 +92,7 @@ sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "t
 import numpy as np, torch, torch.distributed as dist
 import oracle
 from util import oracle_quantize_fn
-from dgx_vllm_b200 import synth
+import synth
 from dgx_vllm_b200.moe_ep import ExpertParallelMoE
 dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()

@@ -79,7 +79,7 @@ def test_dense_and_packed_variants():
 
 
 def _moe_case(E, H, I, B, topk, seed, dtype=torch.bfloat16):
-    from dgx_vllm_b200 import synth
+    import synth
     w13 = synth.make_sparse_experts(E, 2 * I, H, seed, "cpu", oracle_quantize_fn)
     w2 = synth.make_sparse_experts(E, H, I, seed + 1, "cpu", oracle_quantize_fn)
     tw, ids = synth.make_routing(B, E, topk, seed + 2, "cpu")
@@ -115,7 +115,7 @@ def test_fused_moe_layer(B):
 def test_fused_moe_expert_map_and_flags():
     E_local, E_global, H, I, B, topk = 4, 8, 256, 128, 5, 3
     w13, w2, _, _, hidden = _moe_case(E_local, H, I, B, topk, seed=9, dtype=torch.float16)
-    from dgx_vllm_b200 import synth
+    import synth
     tw, ids = synth.make_routing(B, E_global, topk, 10, "cpu")
     emap = np.array([-1, 0, -1, 1, 2, -1, 3, -1], np.int32)       # half of the global experts are local
     out = _run_fused(w13, w2, tw, ids, hidden, I, emap)
@@ -143,7 +143,8 @@ def test_argument_validation():
 def test_ep_records_pack_fused_combine_single_gpu():
     # the expert-parallel kernels without the collectives: two "ranks" emulated on one GPU by
     # swapping the record blocks by hand (what the all-to-all does), against the full-layer oracle
-    from dgx_vllm_b200 import _lib, synth
+    from dgx_vllm_b200 import _lib
+    import synth
     from dgx_vllm_b200._torch_util import workspace
     L = _lib.lib()
     G, E_glob, H, I, B, topk = 2, 8, 256, 128, 5, 3
