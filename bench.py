@@ -37,6 +37,10 @@ E_TOTAL, HIDDEN, INTER, TOPK = 512, 2048, 512, 10
 BYTES_PER_EXPERT_GATE_UP = 2 * INTER * HIDDEN * 7 // 16          # comp 1/4 + meta 1/8 + scale 1/16 B per weight
 BYTES_PER_EXPERT_DOWN = HIDDEN * INTER * 7 // 16
 N_ROUTINGS = 8
+# dram__bytes_read.sum + dram__bytes_write.sum of the gate_up and down GEMV launches of one layer, per routed expert,
+# from the ncu capture whose summary is committed with the profiles (244 routed experts: 233.61 MB + 118.83 MB)
+NCU_TRAFFIC_BYTES_PER_EXPERT = (233.61e6 + 118.83e6) / 244.0
+NCU_TRAFFIC_SOURCE = "ncu capture of the two GEMV launches (batch 32, 244 routed experts), scaled by routed experts"
 
 
 def measured_peaks():
@@ -124,43 +128,50 @@ def build_case(dev, e_local: int, batch: int, rank: int):
     return w13, w2, batches
 
 
-def cpu_baseline(batch: int, max_seconds: float = 25.0):
-    """Times the reference's dequantize-to-bf16 emulation of the same MoE layer on the host cores.
-    The sample is one batch routed over a reduced expert table (same per-expert shapes), repeated
-    until ~max_seconds of CPU work have been spent."""
+def cpu_baseline(batch: int, max_seconds: float = 25.0, steps: int = 5, warmup: int = 1):
+    """Times the reference's dequantize-to-bf16 emulation of the same MoE layer on the host cores (all of them: the
+    thread count is set explicitly, a launcher's OMP_NUM_THREADS=1 would otherwise leave one).  A step is one batch:
+    every routed expert (about 240 of 512 at batch 32) is dequantized and multiplied on its own; the weight values come
+    from a 64-expert table kept on the host (expert id modulo 64), which changes no arithmetic cost.  If `steps` full
+    batches would take longer than max_seconds, a step processes the first rows of the batch only and says so."""
     import torch
     import synth
     from oracle import emulation
     import oracle
     import numpy as np
 
+    torch.set_num_threads(os.cpu_count() or 1)
+
     def qfn(w, gs):
         bits = w.contiguous().view(torch.int16).numpy().view(np.uint16)
         c, s = oracle.quantize_bf16(bits, float(gs[0]))
         return torch.from_numpy(c), torch.from_numpy(s)
 
-    e_cpu = 64                                     # experts materialised on the host for the sample
+    e_cpu = 64                                     # experts materialised on the host
     w13 = synth.make_sparse_experts(e_cpu, 2 * INTER, HIDDEN, 1, "cpu", qfn)
     w2 = synth.make_sparse_experts(e_cpu, HIDDEN, INTER, 2, "cpu", qfn)
     tw, ids = synth.make_routing(batch, E_TOTAL, TOPK, 3, "cpu")
-    uniq_full = int(ids.unique().numel())
-    # remap the routed experts onto the materialised ones without merging them beyond e_cpu:
-    # the active-expert count per step (the cost driver) is min(unique, e_cpu); scale the time up.
-    ids_c = (ids % e_cpu).to(torch.int32)
-    uniq_cpu = int(ids_c.unique().numel())
     hidden = synth.make_hidden(batch, HIDDEN, 4, "cpu")
-    emulation.moe_layer_emulation(hidden[:1], tw[:1], ids_c[:1], w13, w2, INTER)        # warm-up
+    t0 = time.perf_counter()
+    emulation.moe_layer_emulation(hidden[:1], tw[:1], ids[:1], w13, w2, INTER, table_rows=e_cpu)        # warm-up, 10 experts
+    per_expert = (time.perf_counter() - t0) / TOPK
+    uniq_full = int(ids.unique().numel())
+    rows = batch
+    while rows > 1 and per_expert * int(ids[:rows].unique().numel()) * (steps + warmup) > max_seconds:
+        rows = max(1, rows // 2)
+    for _ in range(warmup):
+        emulation.moe_layer_emulation(hidden[:rows], tw[:rows], ids[:rows], w13, w2, INTER, table_rows=e_cpu)
     times = []
-    t_end = time.perf_counter() + max_seconds
-    while len(times) < 5 and (time.perf_counter() < t_end or not times):
+    for _ in range(steps):
         t0 = time.perf_counter()
-        emulation.moe_layer_emulation(hidden, tw, ids_c, w13, w2, INTER)
+        emulation.moe_layer_emulation(hidden[:rows], tw[:rows], ids[:rows], w13, w2, INTER, table_rows=e_cpu)
         times.append(time.perf_counter() - t0)
-    t = statistics.median(times) * (uniq_full / max(uniq_cpu, 1))
-    return {"value": batch / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": (f"one batch of {batch} tokens, {uniq_cpu} active experts materialised on the host "
-                       f"(of {uniq_full} routed), time scaled by {uniq_full}/{uniq_cpu}; "
-                       f"median of {len(times)} runs, per-call weight dequantisation included")}
+    t = statistics.mean(times)
+    uniq = int(ids[:rows].unique().numel())
+    return {"value": rows / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": (f"{steps} steps of {rows} of the batch's {batch} tokens, {uniq} routed experts per step "
+                       f"({uniq_full} for the whole batch), each dequantized and multiplied per step; weight values from a "
+                       f"{e_cpu}-expert host table (id modulo {e_cpu}); mean step {t * 1e3:.1f} ms")}
 
 
 def run_reference(args):
@@ -168,7 +179,7 @@ def run_reference(args):
     if rank != 0:
         return
     import torch
-    cb = cpu_baseline(args.batch, max_seconds=20.0 * max(1, min(args.steps, 3)))
+    cb = cpu_baseline(args.batch, max_seconds=150.0, steps=args.steps, warmup=args.warmup)
     ms = args.batch / cb["value"] * 1e3
     line = {"impl": "reference", "metric": "NVFP4 MoE-layer tokens/s", "value": cb["value"], "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -412,7 +423,8 @@ def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_lay
             w = (0.02 * torch.randn(N, K, generator=gen, device=dev)).to(torch.bfloat16)
             g = synth.global_scale_of(w)
             c, s_ = scaled_fp4_quant(w, g)
-            sh.append((c, s_, g))
+            lin = scaled_fp4_quant(w, g, is_sf_swizzled_layout=False)[1] if li == (layers - 1) % distinct_layers else None
+            sh.append((c, s_, g, lin))        # linear scales of the last layer's set, for the check below
         sets.append((w13, w2, sh))
     emap = torch.empty(0, dtype=torch.int32, device=dev)
     eo1 = lambda B: (torch.tensor([0, B], dtype=torch.int32, device=dev), torch.tensor([0, (B + 127) // 128 * 128], dtype=torch.int32, device=dev))
@@ -426,30 +438,31 @@ def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_lay
         alphas = [((1.0 / (gx * sh[0][2])).float(), (1.0 / (ga * sh[1][2])).float()) for (_, _, sh) in sets]
 
         def stack():
-            acc = None
+            acc = y = z = None
             for l in range(layers):
                 w13, w2, sh = sets[l % distinct_layers]
                 x = xs[l]
                 tw, ids = routes[l]
                 y = sp7.fused_sparse_moe_v7(x, tw, ids, emap, *[w13[k] for k in keys], *[w2[k] for k in keys], I, False)
                 # shared expert: quant -> GEMM -> SiLU*up + quant -> GEMM
-                (c13, s13, g13), (c2, s2, g2) = sh
+                (c13, s13, g13, _), (c2, s2, g2, _) = sh
                 xc, xsf = scaled_fp4_quant(x, gx)
                 al13, al2 = alphas[l % distinct_layers]
                 gu = cutlass_scaled_fp4_mm(xc, c13, xsf, s13, al13, torch.bfloat16)
                 hc, hsf = gm.silu_and_mul_scaled_fp4_experts_quant(gu, ga, offs, bso)
                 z = cutlass_scaled_fp4_mm(hc, c2, hsf, s2, al2, torch.bfloat16)
                 acc = y + z if acc is None else acc + y + z
-            return acc
+            return acc, y, z
 
         for _ in range(2):
             stack()
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            res = stack()
+            res, y_last, z_last = stack()
         graph.replay()
         torch.cuda.synchronize()
+        verified = _verify_stack_last_layer(sets[(layers - 1) % distinct_layers], xs[-1], routes[-1], y_last, z_last, gx, ga, I)
         ts = []
         for _ in range(reps):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -462,11 +475,111 @@ def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_lay
         uniq = statistics.mean(int(r[1].unique().numel()) for r in routes)
         byt = layers * (uniq * (BYTES_PER_EXPERT_GATE_UP + BYTES_PER_EXPERT_DOWN) + (2 * I * H + H * I) * 0.5625)
         out[f"batch_{B}"] = {"tokens_per_s": B / t, "ms_per_token_step": t * 1e3, "us_per_layer": t / layers * 1e6,
-                             "weight_GBps": byt / t / 1e9, "finite": bool(torch.isfinite(res.float()).all().item())}
+                             "weight_GBps": byt / t / 1e9, "finite": bool(torch.isfinite(res.float()).all().item()),
+                             "verified_last_layer": verified}
         del graph
     out["config"] = (f"{layers} layers, {distinct_layers} distinct weight sets cycled, routed 2:4 sparse experts + shared dense "
                      f"NVFP4 expert per layer, one CUDA graph per batch size")
     return out
+
+
+def _rel(got, ref):
+    import numpy as np
+    return float(np.max(np.abs(np.asarray(got, np.float64) - np.asarray(ref, np.float64))) / (np.max(np.abs(ref)) + 1e-30))
+
+
+def _verify_stack_last_layer(wset, x, route, y, z, gx, ga, I, n_tok: int = 2):
+    """The decode stack's last layer on its first tokens, as replayed from the CUDA graph, against the CPU oracle:
+    routed-expert output (<= 1e-2) and shared-expert output (quantize -> GEMM -> SiLU*up + quantize -> GEMM; both GEMM
+    inputs are re-quantized, where single E2M1 codes may flip on a 16-bit rounding, hence the looser figure)."""
+    import numpy as np
+    import oracle
+    from util import bf16_bits, expert_fetch
+    w13, w2, sh = wset
+    tw, ids = route
+    n = min(n_tok, x.shape[0])
+    ref_y = oracle.fused_sparse_moe_by_expert(x[:n].float().cpu().numpy(), tw[:n].cpu().numpy(), ids[:n].cpu().numpy(),
+                                              expert_fetch(w13, w2), I)
+    (c13, _, g13, l13), (c2, _, g2, l2) = sh
+    bf = lambda v: oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(v))
+    u8 = lambda t: t.view(__import__("torch").uint8).cpu().numpy()
+    gu = bf(oracle.nvfp4_linear(bf16_bits(x[:n]), float(gx[0]), c13.cpu().numpy(), u8(l13), float(g13[0])))
+    act = bf((gu[:, :I] / (1.0 + np.exp(-gu[:, :I].astype(np.float64))) * gu[:, I:]).astype(np.float32))
+    ref_z = oracle.nvfp4_linear(oracle.f32_to_bf16_bits(act), float(ga[0]), c2.cpu().numpy(), u8(l2), float(g2[0]))
+    return {"tokens": n, "routed_rel_err": _rel(y[:n].float().cpu().numpy(), ref_y),
+            "shared_rel_err": _rel(z[:n].float().cpu().numpy(), ref_z)}
+
+
+def verify_layer_step(layer, batch0, w13, w2, world, rank, dev, n_tok: int = 4):
+    """One step of the benchmarked layer on rank 0's first tokens against the CPU oracle, outside every timed region.
+    With several ranks every rank evaluates the oracle over its own experts for those tokens and one all-reduce
+    adds the partial rows."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from util import expert_fetch
+    h, tw, ids = batch0
+    out = layer.forward(h, tw, ids)
+    torch.cuda.synchronize()
+    sample = [h[:n_tok].clone(), tw[:n_tok].clone(), ids[:n_tok].clone()]
+    if world > 1:
+        for t in sample:
+            dist.broadcast(t, src=0)
+    hs, ws_, is_ = [t.cpu() for t in sample]
+    emap = layer.expert_map(dev).cpu().numpy()
+    part = oracle.fused_sparse_moe_by_expert(hs.float().numpy(), ws_.numpy(), emap[is_.numpy()], expert_fetch(w13, w2), INTER)
+    ref = torch.from_numpy(part).to(dev)
+    if world > 1:
+        dist.all_reduce(ref)
+    if rank != 0:
+        return None
+    return {"tokens": n_tok, "rel_err": _rel(out[:n_tok].float().cpu().numpy(), ref.cpu().numpy()),
+            "against": "CPU oracle (fp32 dequantize-then-matmul per routed expert), max|diff|/max|ref|"}
+
+
+def bench_reference_v7_gpu(dev, w13, w2, batches, flush, ours, steps: int = 20):
+    """The reference's own CUDA extension (sparse_fp4_kernel/sparse_fp4_v7.cu compiled unmodified for sm_100 by
+    oracle/build_ref_v7.py) on the same tensors, inside its contract (identity expert_map, N >= 512; its lazy table
+    initialisation happens in the warm-up calls).  Cold: L2 flushed before every layer, CUDA events; loop: back to back."""
+    import torch
+    from oracle import build_ref_v7
+    mod = build_ref_v7.load()
+    if mod is None:
+        return {"unavailable": "oracle/_ref/sparse_fp4_v7 not built (oracle/build_ref_v7.py needs a checkout of the reference)"}
+    k = ("comp_T", "meta_T", "scale_T", "g_scales")
+    emap = torch.empty(0, dtype=torch.int32, device=dev)
+    wargs = [w13[x] for x in k] + [w2[x] for x in k]
+
+    def run(i):
+        h, tw, ids = batches[i % N_ROUTINGS]
+        return mod.fused_sparse_moe_v7(h, tw, ids, emap, *wargs, INTER, False)
+
+    for i in range(3):
+        theirs = run(i)
+    torch.cuda.synchronize()
+    cold = []
+    for i in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        run(i)
+        b.record()
+        torch.cuda.synchronize()
+        cold.append(a.elapsed_time(b) * 1e-3)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        run(i)
+    b.record()
+    torch.cuda.synchronize()
+    loop = a.elapsed_time(b) * 1e-3 / steps
+    B = batches[0][0].shape[0]
+    theirs = run(0).float()
+    mine = ours(*batches[0]).float()
+    return {"us_per_layer_cold_l2": statistics.mean(cold) * 1e6, "us_per_layer_back_to_back": loop * 1e6,
+            "tokens_per_s_back_to_back": B / loop, "rel_diff_to_this_library": _rel(mine.cpu().numpy(), theirs.cpu().numpy()),
+            "kernel": "fused_sparse_moe_v7 of the reference (batched_sparse_v7_kernel x 2 + 5 glue kernels), built with -arch sm_100"}
 
 
 def config_dict(args):
@@ -486,6 +599,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-mode", default="gather", choices=["gather", "a2a"],
+                    help="expert-parallel exchange: all-gather + reduce-scatter (default) or all-to-all both ways")
     ap.add_argument("--no-parts", action="store_true", help="skip the dense GEMM / quantizer side measurements")
     ap.add_argument("--only-prefill", action="store_true",
                     help="run just the grouped prefill layer (the `moe_prefill_8192_tokens` part) and print its numbers; "
@@ -527,7 +642,7 @@ def main():
         sampler.start()
     e_local = E_TOTAL // world
     w13, w2, batches = build_case(dev, e_local, args.batch, rank)
-    layer = ExpertParallelMoE(E_TOTAL, INTER, w13, w2)
+    layer = ExpertParallelMoE(E_TOTAL, INTER, w13, w2, mode=args.ep_mode)
     B = args.batch
     hbm_peak, peak_kind = measured_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -543,6 +658,8 @@ def main():
 
     for i in range(args.warmup):
         step(i)
+    barrier()
+    verified = verify_layer_step(layer, batches[0], w13, w2, world, rank, dev)
     barrier()
 
     # ---- value: K steps back to back, device-timed
@@ -563,25 +680,35 @@ def main():
     ms_step = float(t.item()) / args.steps
     value = B * world / (ms_step * 1e-3)
 
-    # ---- roofline: per-launch duration of the two GEMV kernels, cold L2 (flush between steps)
+    # ---- roofline: per-launch duration of the two GEMV kernels, cold L2 (flush between steps), measured on the
+    # very call the step makes: with several ranks that is the local layer over the records of ALL ranks' tokens
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    uniq = []
+    pev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)] if world > 1 else None
+    uniq, local_pairs = [], []
+    emap_all = layer.expert_map(dev)
+    for r in range(N_ROUTINGS):
+        ids = batches[r][2]
+        if world > 1:
+            all_ids = torch.empty((world * B, TOPK), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(all_ids, ids.contiguous())
+        else:
+            all_ids = ids
+        m = emap_all[all_ids.long()]
+        uniq.append(int(m[m >= 0].unique().numel()))
+        local_pairs.append(int((m >= 0).sum().item()))
+    uniq = [uniq[i % N_ROUTINGS] for i in range(args.steps)]
+    local_pairs = [local_pairs[i % N_ROUTINGS] for i in range(args.steps)]
     for i in range(args.steps):
-        h, tw, ids = batches[i % N_ROUTINGS]
-        emap = layer.expert_map(dev)
         flush.zero_()
+        if world > 1:
+            dist.barrier()
         for e in evs[i]:
             e.record()      # creates the underlying CUDA events; the library re-records them
         L.b200fp4_fused_moe_profile_events(evs[i][0].cuda_event, evs[i][1].cuda_event, evs[i][2].cuda_event)
-        if world == 1:
-            step(i)
-            uniq.append(int(ids.unique().numel()))
-        else:
-            # local part only: the GEMV kernels see the tokens of all ranks; count this rank's experts
-            k = ("comp_T", "meta_T", "scale_T", "g_scales")
-            sp7.fused_sparse_moe_v7(h, tw, ids, emap, *[w13[x] for x in k], *[w2[x] for x in k], INTER, False)
-            m = emap[ids.long()]
-            uniq.append(int(m[m >= 0].unique().numel()))
+        if pev:
+            layer.phase_events = pev[i]
+        step(i)
+        layer.phase_events = None
         L.b200fp4_fused_moe_profile_events(0, 0, 0)
     torch.cuda.synchronize()
     # events 0 -> 2 bracket the two projections of the layer's default path (two launches at this batch
@@ -591,6 +718,8 @@ def main():
     k4 = ("comp_T", "meta_T", "scale_T", "g_scales")
     n_sep = min(args.steps, 16)
     evs2 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_sep)]
+    if world > 1:
+        n_sep = 0          # the per-projection split is a one-GPU side measurement
     for i in range(n_sep):
         h, tw, ids = batches[i % N_ROUTINGS]
         flush.zero_()
@@ -603,25 +732,34 @@ def main():
     torch.cuda.synchronize()
     t_gu = [evs2[i][0].elapsed_time(evs2[i][1]) * 1e-3 for i in range(n_sep)]
     t_dn = [evs2[i][1].elapsed_time(evs2[i][2]) * 1e-3 for i in range(n_sep)]
-    pairs = B * TOPK
-    # algorithmic bytes per launch: weights of the unique experts + activations in/out per pair
-    b_gu = [u * BYTES_PER_EXPERT_GATE_UP + pairs * (HIDDEN * 2 + INTER * 2) for u in uniq]
-    b_dn = [u * BYTES_PER_EXPERT_DOWN + pairs * (INTER * 2 + HIDDEN * 4) for u in uniq]
+    # algorithmic bytes per launch: weights of the unique local experts + activations in/out per local pair
+    b_gu = [u * BYTES_PER_EXPERT_GATE_UP + p * (HIDDEN * 2 + INTER * 2) for u, p in zip(uniq, local_pairs)]
+    b_dn = [u * BYTES_PER_EXPERT_DOWN + p * (INTER * 2 + HIDDEN * 4) for u, p in zip(uniq, local_pairs)]
     ach = (sum(b_gu) + sum(b_dn)) / sum(t_both) / 1e9
-    # DRAM traffic of the two projections from the ncu capture summarised in
-    # profiles/sparse_gemv_mma_moe_decode_b32.md: 233.6 MB + 118.8 MB read+written for 244 routed experts
-    # (1.03 x the algorithmic bytes); it grows with the number of routed experts, so it is scaled to this run's mean
-    traffic = (233.61e6 + 118.83e6) / 244.0 * statistics.mean(uniq)
+    # DRAM traffic (dram__bytes_read + dram__bytes_write of the two projections) is not measurable inside this run; the
+    # figure is the ratio of an ncu capture of the same two kernels on a smaller case of this workload (NCU_TRAFFIC below:
+    # bytes per routed expert) scaled to this run's routed experts -- traffic grows in proportion to them.
+    traffic = NCU_TRAFFIC_BYTES_PER_EXPERT * statistics.mean(uniq) if world == 1 else None
     roofline = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-                "traffic": traffic, "peak_kind": f"{peak_kind} copy bandwidth",
+                "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE if world == 1 else None,
+                "peak_kind": f"{peak_kind} copy bandwidth",
                 "kernel": "sparse_gemv_mma_kernel: gate_up+SiLU and down projections of one layer (tensor-core 2:4 GEMV)",
-                "per_launch_us": {"both_projections": statistics.mean(t_both) * 1e6,
-                                  "gate_up_separate_launch": statistics.mean(t_gu) * 1e6,
-                                  "down_separate_launch": statistics.mean(t_dn) * 1e6},
+                "per_launch_us": {"both_projections": statistics.mean(t_both) * 1e6},
                 "algorithmic_bytes_per_step": (sum(b_gu) + sum(b_dn)) / args.steps,
-                "gate_up_GBps_separate_launch": sum(b_gu[:n_sep]) / sum(t_gu) / 1e9,
-                "down_GBps_separate_launch": sum(b_dn[:n_sep]) / sum(t_dn) / 1e9,
-                "unique_experts_mean": statistics.mean(uniq)}
+                "unique_experts_mean": statistics.mean(uniq), "local_pairs_mean": statistics.mean(local_pairs)}
+    if n_sep:
+        roofline["per_launch_us"].update({"gate_up_separate_launch": statistics.mean(t_gu) * 1e6,
+                                          "down_separate_launch": statistics.mean(t_dn) * 1e6})
+        roofline["gate_up_GBps_separate_launch"] = sum(b_gu[:n_sep]) / sum(t_gu) / 1e9
+        roofline["down_GBps_separate_launch"] = sum(b_dn[:n_sep]) / sum(t_dn) / 1e9
+    ep_phases = None
+    if pev:
+        # device time of the four phases of the expert-parallel step (cold L2, ranks released by a barrier), max over ranks
+        ph = torch.tensor([[pev[i][j].elapsed_time(pev[i][j + 1]) * 1e3 for j in range(4)] for i in range(args.steps)],
+                          dtype=torch.float64, device=dev).mean(0)
+        dist.all_reduce(ph, op=dist.ReduceOp.MAX)
+        ep_phases = dict(zip(("pack_us", "dispatch_us", "local_layer_us", "combine_us"), [float(x) for x in ph.tolist()]))
+        ep_phases["mode"] = args.ep_mode
 
     # ---- e2e: host buffers in, host result out, through the public op
     host = []
@@ -664,11 +802,17 @@ def main():
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16 products, f32 accumulate (NVFP4 weights, bf16 activations)",
                 "data": "synthetic", "config": config_dict(args), "roofline": roofline,
                 "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-                "gpu_launches": launches, "clocks": clocks}
+                "gpu_launches": launches, "clocks": clocks, "verified": verified}
+        if ep_phases:
+            line["ep_phases"] = ep_phases
+        ref_gpu = None
+        if world == 1 and not args.no_parts:
+            ref_gpu = bench_reference_v7_gpu(dev, w13, w2, batches, flush, layer.forward)
         if world == 1 and not args.no_parts:
             del w13, w2, layer
             torch.cuda.empty_cache()
             line["parts"] = bench_dense_parts(dev, flush, hbm_peak)
+            line["parts"]["reference_v7_gpu"] = ref_gpu
             torch.cuda.empty_cache()
             line["parts"]["moe_prefill_8192_tokens"] = bench_moe_prefill(dev, flush, hbm_peak)
             torch.cuda.empty_cache()

@@ -1565,7 +1565,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
       !w2_scale || !w2_g)
     return B200FP4_STATUS_INVALID_VALUE;
   if (expert_map && global_E <= 0) return B200FP4_STATUS_INVALID_VALUE;
-  if (E > kPlanMaxExperts || out_dtype == B200FP4_DTYPE_F32) return B200FP4_STATUS_NOT_SUPPORTED;
+  if (E > kPlanMaxExperts) return B200FP4_STATUS_NOT_SUPPORTED;
   SparseWeights w13, w2;
   w13.comp = w13_comp; w13.meta = w13_meta; w13.scale = w13_scale; w13.g = w13_g;
   w13.comp_e = (H / 4) * 2 * I; w13.comp_pair = 4 * I; w13.comp_odd = 2 * I;

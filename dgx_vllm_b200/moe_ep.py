@@ -1,21 +1,24 @@
 """Expert-parallel MoE layers: E/G experts per GPU.
 
-Decode (`ExpertParallelMoE`): token dispatch and combine with one all-to-all each way over NCCL
-(NVLink / NVSwitch), local compute by the fused sparse MoE op.
-Prefill (`ExpertParallelMoEPrefill`): with thousands of tokens and top-10 of 512 experts nearly every
-token has an expert on every rank, so dispatch is an all-gather of the token block and combine a
-reduce-scatter of the partial output rows; local compute is the grouped NVFP4 path.
+Decode (`ExpertParallelMoE`): every rank packs its tokens into dispatch records (activation row, top-k
+global expert ids, router weights), one all-gather brings all ranks' records to every rank, the fused
+sparse MoE op runs over them with `expert_map` masking the experts the rank does not own (-1 entries
+are skipped by the plan kernel, so foreign pairs cost no weight traffic) and writes fp32 partial rows,
+and one reduce-scatter sums the partial rows of a token over the ranks and leaves each rank its own
+tokens.  With top-10 of 512 experts a token has an expert on nearly every rank, so "send a token only
+where it is needed" saves nothing over the all-gather, which is a single NCCL kernel over NVLink /
+NVSwitch instead of G-1 sends and receives per rank; the sizes are fixed, so no split-size exchange or
+host round trip sits on the decode path.  `mode="a2a"` keeps the earlier spelling (fixed-capacity
+all-to-all dispatch of G copies, all-to-all of 16-bit partial rows, fp32 sum at the source) for
+comparison.
+Prefill (`ExpertParallelMoEPrefill`): all-gather of the token block, grouped NVFP4 path over the local
+experts, reduce-scatter of the partial output rows.
 
 The reference has no multi-GPU code of its own (it serves with tensor parallelism through vLLM);
 this layout is the one the path's shard rule prescribes: experts [r*E/G, (r+1)*E/G) live on rank r.
 
-Dispatch uses fixed-capacity slots so that no host round trip (split-size exchange + .tolist())
-sits on the decode path and the step stays CUDA-graph friendly: every rank sends each peer one
-record per local token -- the token's activation row, its top-k global expert ids and router
-weights packed in one byte buffer -- and the receiving rank masks the experts it does not own
-through `expert_map` (-1 entries are skipped by the GEMV plan kernel, so foreign pairs cost no
-weight traffic).  Combine returns one partial output row per (source token, owner rank); the
-source rank adds the G partial rows in fp32.
+Limits: the fused layer takes at most 65535 (token, expert) pairs per call, i.e. G*B*topk <= 65535
+(B <= 819 tokens per rank at 8 ranks and top-10); `forward` raises before anything is enqueued.
 """
 from __future__ import annotations
 
@@ -53,23 +56,32 @@ def unpack_records(rec: torch.Tensor, H: int, topk: int, dtype: torch.dtype):
 class ExpertParallelMoE:
     """One MoE layer sharded over the ranks of `group`.
 
-    With CUDA tensors the step is: ep_pack kernel -> all_to_all -> fused sparse MoE reading the
-    received records in place -> all_to_all -> ep_combine kernel (7 launches + 2 collectives).
+    With CUDA tensors the step is: ep_pack kernel -> all_gather -> fused sparse MoE reading the
+    gathered records in place (fp32 partial rows) -> reduce_scatter -> cast (5 launches of this
+    library + 2 collectives); mode="a2a": ep_pack (G copies) -> all_to_all -> fused layer (16-bit
+    partial rows) -> all_to_all -> ep_combine.
 
     `local_moe_fn(hidden [T,H], topk_w [T,topk] f32, topk_ids [T,topk] i32 (global ids),
     expert_map [global_E] i32) -> [T,H]`, when given, replaces the CUDA ops and the torch
-    packing path is used instead (this is how the dispatch/combine logic is tested on CPU ranks)."""
+    packing path is used instead (this is how the dispatch/combine logic is tested on CPU ranks).
+
+    `phase_events`: when set to a list of five CUDA events, forward records them before the pack, after
+    it, after the dispatch collective, after the local layer and after the combine (benchmark hook)."""
 
     def __init__(self, global_E: int, inter: int, w13: Optional[dict], w2: Optional[dict], group=None,
-                 local_moe_fn: Optional[Callable] = None):
+                 local_moe_fn: Optional[Callable] = None, mode: str = "gather"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if global_E % self.world != 0:
             raise RuntimeError("the number of experts must be divisible by the number of ranks")
+        if mode not in ("gather", "a2a"):
+            raise RuntimeError("mode must be 'gather' or 'a2a'")
         self.global_E = global_E
         self.inter = inter
         self.w13, self.w2 = w13, w2
+        self.mode = mode
+        self.phase_events = None
         self._emap = None
         self._fn = local_moe_fn
         self._bufs = {}
@@ -93,6 +105,18 @@ class ExpertParallelMoE:
         topk = topk_ids.shape[1]
         G = self.world
         rec = pack_records(hidden, topk_w, topk_ids)                       # [B, R]
+        if self.mode == "gather":
+            recv = torch.empty((G * B, rec.shape[1]), dtype=torch.uint8, device=rec.device)
+            dist.all_gather_into_tensor(recv, rec.contiguous(), group=self.group)                # dispatch
+            h_all, w_all, ids_all = unpack_records(recv, H, topk, hidden.dtype)
+            part = self._fn(h_all, w_all, ids_all, emap).float().contiguous()   # [G*B, H] fp32 partial rows
+            if dist.get_backend(self.group) == "gloo":                          # gloo has no reduce-scatter
+                dist.all_reduce(part, group=self.group)
+                out = part[self.rank * B:(self.rank + 1) * B]
+            else:
+                out = torch.empty((B, H), dtype=torch.float32, device=part.device)
+                dist.reduce_scatter_tensor(out, part, group=self.group)                         # combine
+            return out.to(hidden.dtype)
         send = rec.unsqueeze(0).expand(G, B, rec.shape[1]).contiguous()    # one slot block per peer
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv.view(G * B, -1), send.view(G * B, -1), group=self.group)     # dispatch
@@ -111,39 +135,65 @@ class ExpertParallelMoE:
         G = self.world
         L = _lib.lib()
         require(hidden.is_contiguous() and hidden.dtype in (torch.bfloat16, torch.float16), "hidden must be contiguous 16-bit")
+        require(G * B * topk <= 65535, "the fused layer takes at most 65535 (token, expert) pairs: G*B*topk is larger")
         ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
         ids = ids.contiguous()
         tw = topk_w if topk_w.dtype == torch.float32 else topk_w.float()
         tw = tw.contiguous()
         R = L.b200fp4_ep_record_bytes(H, topk)
-        key = (dev.index, B, H, topk, hidden.dtype)
+        gather = self.mode == "gather"
+        key = (dev.index, B, H, topk, hidden.dtype, self.mode)
         bufs = self._bufs.get(key)
         if bufs is None:
-            bufs = (torch.empty(G * B * R, dtype=torch.uint8, device=dev), torch.empty(G * B * R, dtype=torch.uint8, device=dev),
-                    torch.empty(G * B, H, dtype=hidden.dtype, device=dev), torch.empty(G * B, H, dtype=hidden.dtype, device=dev))
+            if gather:
+                bufs = (torch.empty(B * R, dtype=torch.uint8, device=dev), torch.empty(G * B * R, dtype=torch.uint8, device=dev),
+                        torch.empty(G * B, H, dtype=torch.float32, device=dev), torch.empty(B, H, dtype=torch.float32, device=dev))
+            else:
+                bufs = (torch.empty(G * B * R, dtype=torch.uint8, device=dev), torch.empty(G * B * R, dtype=torch.uint8, device=dev),
+                        torch.empty(G * B, H, dtype=hidden.dtype, device=dev), torch.empty(G * B, H, dtype=hidden.dtype, device=dev))
             self._bufs[key] = bufs
         send, recv, part, back = bufs
         T = G * B
         E = self.global_E // G
         k = ("comp_T", "meta_T", "scale_T", "g_scales")
         ws = workspace(dev, L.b200fp4_fused_moe_workspace_bytes(T, topk, H, self.inter, E))
-        out = torch.empty(B, H, dtype=hidden.dtype, device=dev)
         code = dtype_code(hidden.dtype)
         if self._flags is None:   # ordered metadata -> tensor-core GEMVs; checked once per layer
             from .sparse_fp4_v7 import metadata_ordered
             ok = metadata_ordered(self.w13["meta_T"]) and metadata_ordered(self.w2["meta_T"])
             self._flags = _lib.SPARSE_META_ORDERED if ok else 0
+            self._wptrs = ([ptr(self.w13[x]) for x in k] + [self.w13["scale_T"].shape[1]] +
+                           [ptr(self.w2[x]) for x in k] + [self.w2["scale_T"].shape[1]])
+        ev = self.phase_events
+        st = torch.cuda.current_stream(dev)
         with torch.cuda.device(dev):
-            _lib.check(L.b200fp4_ep_pack(ptr(hidden), ptr(ids), ptr(tw), B, H, topk, G, ptr(send), stream_ptr(dev)), "ep_pack")
-            dist.all_to_all_single(recv, send, group=self.group)                                   # dispatch
+            if ev:
+                ev[0].record(st)
+            _lib.check(L.b200fp4_ep_pack(ptr(hidden), ptr(ids), ptr(tw), B, H, topk, 1 if gather else G, ptr(send),
+                                         st.cuda_stream), "ep_pack")
+            if ev:
+                ev[1].record(st)
+            if gather:
+                dist.all_gather_into_tensor(recv, send, group=self.group)                          # dispatch
+            else:
+                dist.all_to_all_single(recv, send, group=self.group)
+            if ev:
+                ev[2].record(st)
             _lib.check(L.b200fp4_fused_sparse_moe_records(
-                ptr(recv), R, code, ptr(emap), emap.numel(),
-                *[ptr(self.w13[x]) for x in k], self.w13["scale_T"].shape[1],
-                *[ptr(self.w2[x]) for x in k], self.w2["scale_T"].shape[1],
-                ptr(part), code, T, topk, H, self.inter, E, self._flags, ptr(ws), ws.numel(), stream_ptr(dev)),
-                "fused_sparse_moe_records")
-            dist.all_to_all_single(back, part, group=self.group)                                   # combine
-            _lib.check(L.b200fp4_ep_combine(ptr(back), code, B, H, G, ptr(out), stream_ptr(dev)), "ep_combine")
+                ptr(recv), R, code, ptr(emap), emap.numel(), *self._wptrs,
+                ptr(part), dtype_code(part.dtype), T, topk, H, self.inter, E, self._flags, ptr(ws), ws.numel(),
+                st.cuda_stream), "fused_sparse_moe_records")
+            if ev:
+                ev[3].record(st)
+            if gather:
+                dist.reduce_scatter_tensor(back, part, group=self.group)                           # combine
+                out = back.to(hidden.dtype)
+            else:
+                dist.all_to_all_single(back, part, group=self.group)
+                out = torch.empty(B, H, dtype=hidden.dtype, device=dev)
+                _lib.check(L.b200fp4_ep_combine(ptr(back), code, B, H, G, ptr(out), st.cuda_stream), "ep_combine")
+            if ev:
+                ev[4].record(st)
         return out
 
     def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:

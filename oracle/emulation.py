@@ -96,15 +96,20 @@ def expand_sparse_expert(comp_T: torch.Tensor, meta_T: torch.Tensor, scale_T: to
 
 
 def moe_layer_emulation(hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor, w13: dict, w2: dict,
-                        inter: int) -> torch.Tensor:
+                        inter: int, table_rows: int | None = None) -> torch.Tensor:
     """One MoE layer on the CPU: for every active expert dequantize both projections to the
     activation dtype, run its tokens through gate_up -> SiLU*up -> down, accumulate the
-    router-weighted result in fp32."""
+    router-weighted result in fp32.
+
+    table_rows: the weight tables hold only this many experts and expert id x reads row x % table_rows
+    (the timed baseline keeps a small table on the host; every routed expert is still dequantized and
+    multiplied on its own, so the work per step is that of the full table)."""
     M, H = hidden.shape
     out = torch.zeros(M, H, dtype=torch.float32)
     ids = topk_ids.long()
-    for e in ids.unique().tolist():
-        tok, slot = (ids == e).nonzero(as_tuple=True)
+    for x in ids.unique().tolist():
+        tok, slot = (ids == x).nonzero(as_tuple=True)
+        e = x if table_rows is None else x % table_rows
         W13 = expand_sparse_expert(w13["comp_T"][e], w13["meta_T"][e], w13["scale_T"][e], float(w13["g_scales"][e]), hidden.dtype)
         W2 = expand_sparse_expert(w2["comp_T"][e], w2["meta_T"][e], w2["scale_T"][e], float(w2["g_scales"][e]), hidden.dtype)
         gu = hidden[tok] @ W13.t()
