@@ -51,7 +51,8 @@ struct SparseWeights {
 };
 
 struct Plan {
-  int* hdr;        // [0] = number of unique experts, [1] = number of passes
+  int* hdr;        // [0] = number of unique experts, [1] = number of passes, [2] and [4] = work-item counters of the
+                   // warp-scheduled GEMV (one per projection), [3] = status word of the one-launch layer
   int* pairs;      // [P]  pair indices grouped by expert
   int* mapped;     // [P]  local expert id of each pair, or -1
   int4* pass_rec;  // [passes][2]: {expert, n_tokens, pair0, pair1}, {pair2, pair3, index of pair0 in pairs[], -}
@@ -75,23 +76,56 @@ struct GemvArgs {
 
 // ------------------------------------------------------------------------------------------ plan
 
-// Block 0 builds the plan; the remaining blocks (if any) convert a bf16 activation matrix to fp16.
+// Activation copy modes of the plan kernel's extra blocks.
+//   kConvBf16      bf16 -> fp16, same element order
+//   kConvBf16Frag  bf16 -> fp16 in "fragment order" (below)
+//   kConvF16Frag   fp16 copy in fragment order
+// Fragment order: inside every group of 32 elements (16 words of two halves) word 4i + t is stored at position
+// 4t + i (a 4 x 4 transpose of words).  The 16 bytes at offset 16t of a group are then exactly the four B-operand
+// registers of lane t of a quad for one 32-wide k-step of mma.m16n8k32, which the warp-scheduled GEMV fetches with a
+// single 16-byte asynchronous copy per lane.
+enum { kConvNone = 0, kConvBf16 = 1, kConvBf16Frag = 2, kConvF16Frag = 3 };
+
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
+  const __half2 h = __float22half2_rn(__bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w)));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Block 0 builds the plan; the remaining blocks (if any) copy / convert the activation matrix to fp16.
 __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
-                    Plan plan, const __nv_bfloat16* __restrict__ conv_src, __half* __restrict__ conv_dst,
+                    Plan plan, const void* __restrict__ conv_src_v, __half* __restrict__ conv_dst,
                     int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks,
-                    int* zero_buf, int zero_count, int max_tok) {
+                    int* zero_buf, int zero_count, int max_tok, int conv_mode) {
   if (blockIdx.x > 0) {
+    const uint4* conv_src = reinterpret_cast<const uint4*>(conv_src_v);
     const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
-    for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
-      // rows of the source may be strided (conv_ld_chunks 16-byte chunks apart); the copy is dense
-      const int64_t row = i / conv_row_chunks, col = i - row * conv_row_chunks;
-      const uint4 raw = reinterpret_cast<const uint4*>(conv_src)[row * conv_ld_chunks + col];
-      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-      __half2 h[4];
+    if (conv_mode == kConvBf16) {
+      for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < conv_chunks; i += stride) {
+        // rows of the source may be strided (conv_ld_chunks 16-byte chunks apart); the copy is dense
+        const int64_t row = i / conv_row_chunks, col = i - row * conv_row_chunks;
+        const uint4 raw = conv_src[row * conv_ld_chunks + col];
+        reinterpret_cast<uint4*>(conv_dst)[i] =
+            make_uint4(bf16x2_to_f16x2(raw.x), bf16x2_to_f16x2(raw.y), bf16x2_to_f16x2(raw.z), bf16x2_to_f16x2(raw.w));
+      }
+    } else {
+      // one thread per group of 32 elements: four 16-byte loads, a 4 x 4 word transpose, four 16-byte stores
+      const int64_t groups = conv_chunks >> 2, row_groups = conv_row_chunks >> 2;
+      for (int64_t i = (int64_t)(blockIdx.x - 1) * kPlanThreads + threadIdx.x; i < groups; i += stride) {
+        const int64_t row = i / row_groups, col = i - row * row_groups;
+        uint4 r[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) h[k] = __float22half2_rn(__bfloat1622float2(b2[k]));
-      reinterpret_cast<uint4*>(conv_dst)[i] = *reinterpret_cast<uint4*>(h);
+        for (int k = 0; k < 4; ++k) {
+          r[k] = conv_src[row * conv_ld_chunks + col * 4 + k];
+          if (conv_mode == kConvBf16Frag)
+            r[k] = make_uint4(bf16x2_to_f16x2(r[k].x), bf16x2_to_f16x2(r[k].y), bf16x2_to_f16x2(r[k].z), bf16x2_to_f16x2(r[k].w));
+        }
+        uint4* dst = reinterpret_cast<uint4*>(conv_dst) + i * 4;
+        dst[0] = make_uint4(r[0].x, r[1].x, r[2].x, r[3].x);
+        dst[1] = make_uint4(r[0].y, r[1].y, r[2].y, r[3].y);
+        dst[2] = make_uint4(r[0].z, r[1].z, r[2].z, r[3].z);
+        dst[3] = make_uint4(r[0].w, r[1].w, r[2].w, r[3].w);
+      }
     }
     return;
   }
@@ -100,7 +134,7 @@ __global__ void __launch_bounds__(kPlanThreads)
   const int tid = threadIdx.x;
   for (int e = tid; e < E; e += kPlanThreads) s_count[e] = 0;
   for (int i = tid; i < zero_count; i += kPlanThreads) zero_buf[i] = 0;   // per-pass counters of the one-launch layer
-  if (tid == 0) plan.hdr[3] = 0;
+  if (tid == 0) plan.hdr[2] = plan.hdr[3] = plan.hdr[4] = 0;
   __syncthreads();
   for (int p = tid; p < P; p += kPlanThreads) {
     int e = ids[(int64_t)(p / ids_topk) * ids_ld + (p % ids_topk)];   // ids rows may be strided
@@ -985,6 +1019,241 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
   gemv_mma_phase<CGB, SB, false, 2, TM>(gb, smem, done, need);
 }
 
+// ------------------------------------------------------------------------------------------ warp-scheduled tensor-core GEMV
+//
+// The same arithmetic as gemv_mma_phase (mma.sp m16n8k32, hardware E2M1 / E4M3 decode), organised so that a warp
+// never has to meet another warp:
+//   * a work item is (pass of up to eight tokens, group of 128 output columns) over the WHOLE K, owned by one warp:
+//     no K-slices, so no partial sums in shared memory, no block-wide barrier and no block-wide epilogue;
+//   * warps take items from a global counter (atomicAdd by lane 0), always holding the next item while they
+//     compute the current one, so the tail of the launch is at most one item long whatever the routing;
+//   * the activations are not staged per block: the plan kernel (or the gate_up epilogue) leaves them in
+//     "fragment order" (see kConv*), and each lane copies the 16 bytes that are its own B-operand registers for a
+//     k-step asynchronously into its ring stage, next to the weights of that step;
+//   * a ring stage is one 32-wide k-step: 8 compressed rows, 4 metadata rows and 2 scale rows of 128 columns
+//     (1792 bytes) + 512 bytes of B fragments.  Four stages per warp; the copy for step j+4 is issued into the slot
+//     of step j as soon as step j's shared-memory reads are done, so that four steps are in flight per warp and the
+//     slot of every step is a compile-time constant in the loop unrolled by four (K is a multiple of 128).  The
+//     stream runs across item boundaries.
+//   * 16-byte chunks are XOR-swizzled inside the compressed and metadata rows so that the fragment loads
+//     (rows t and t+4 for lane t of a quad; metadata rows 2(t%2), 2(t%2)+1) touch every bank once.
+// Epilogue from registers: the lane that holds 16 consecutive columns of a token writes them with 16-byte stores;
+// with SiLU the warp's 128 columns are 64 gate + the matching 64 up columns, the two halves of the warp swap one
+// token's values through shuffles, and SiLU(gate)*up leaves in fragment order for the down projection.
+constexpr int kWsThreads = 512;
+constexpr int kWsWarps = 16;
+constexpr int kWsStages = 4;
+constexpr int kWsStageBytes = 1792 + 512;
+constexpr size_t kWsSmemBytes = (size_t)kWsWarps * kWsStages * kWsStageBytes + 128;
+
+struct WsFetch {
+  const uint8_t *pc, *pm, *ps;   // this lane's chunk of compressed row fr, metadata row fr, scale row fr at k-step 0
+  const __half* pb;              // this lane's B fragment at k-step 0
+  bool valid;
+};
+
+template <bool kSilu, int kN>
+__global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const GemvArgs g, int* counter) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q = lane >> 2, t = lane & 3;
+  const int fr = lane >> 3, fc = lane & 7;
+  const int N = kN ? kN : g.N;
+  const int nblk = g.K >> 7;                 // blocks of four 32-wide k-steps
+  const int groups = g.n_slabs;              // 128-column groups per pass
+  const int n_items = g.plan.hdr[1] * groups;
+  const uint32_t ring = ((shared_addr(smem) + 127u) & ~127u) + (uint32_t)warp * (kWsStages * kWsStageBytes);
+
+  // lane-constant shared-memory offsets inside a stage: where this lane's copies land ...
+  const uint32_t d_comp = (uint32_t)fr * 128u + (uint32_t)((fc ^ (2 * (fr & 3))) << 4);
+  const uint32_t d_meta = 1024u + (uint32_t)fr * 128u + (uint32_t)((fc ^ (4 * (fr >> 1))) << 4);
+  const uint32_t d_scale = 1536u + (uint32_t)fr * 128u + (uint32_t)fc * 16u;
+  const uint32_t d_b = 1792u + (uint32_t)lane * 16u;
+  // ... and where its fragments are read from
+  const uint32_t off_comp = (uint32_t)t * 128u + (uint32_t)((q ^ (2 * t)) << 4);
+  const uint32_t off_meta = 1024u + (uint32_t)(2 * (t & 1)) * 128u + (uint32_t)((q ^ (4 * (t & 1))) << 4) + (uint32_t)(t >> 1) * 8u;
+  const uint32_t off_scale = 1536u + (uint32_t)q * 16u;
+
+  auto claim = [&]() {
+    int v = 0;
+    if (lane == 0) v = atomicAdd(counter, 1);
+    return __shfl_sync(0xffffffffu, v, 0);
+  };
+  // what the compute side needs to know about an item
+  struct Item {
+    int e, nt, s0, grp;
+  };
+  auto describe = [&](int it, Item& d, WsFetch& f) {
+    f.valid = it < n_items;
+    if (!f.valid) return;
+    const int pass = it / groups;
+    d.grp = it - pass * groups;
+    const int4 x = g.plan.pass_rec[2 * pass], y = g.plan.pass_rec[2 * pass + 1];
+    d.e = x.x;
+    d.nt = x.y;
+    d.s0 = y.z;
+    // B column q = token q of the pass; columns past the last token repeat token 0 (their results are never stored)
+    const uint32_t pr = (uint32_t)g.plan.pairs[d.s0 + (q < d.nt ? q : 0)];
+    const int64_t row = g.a_magic ? (int64_t)__umulhi(pr, g.a_magic) : (int64_t)pr;
+    f.pb = g.A + row * g.lda + t * 8;
+    int col;
+    if (kSilu) col = fc < 4 ? d.grp * 64 + fc * 16 : g.inter + d.grp * 64 + (fc - 4) * 16;
+    else col = d.grp * 128 + fc * 16;
+    const int64_t lane_off = (int64_t)fr * N + col;
+    f.pc = g.w.comp + ((int64_t)d.e * g.w.comp_e + lane_off);
+    f.pm = g.w.meta + ((int64_t)d.e * g.w.meta_e + lane_off);
+    f.ps = g.w.scale + ((int64_t)d.e * g.w.scale_e + lane_off);
+  };
+  // copies of k-step `u` (relative to f) into ring slot u; always one commit group, so that the wait counts stay fixed
+  auto fetch = [&](const WsFetch& f, int u) {
+    if (f.valid) {
+      const uint32_t dst = ring + (uint32_t)u * kWsStageBytes;
+      const uint8_t* c = f.pc + (int64_t)u * 8 * N;
+      cp_async16_s(dst + d_comp, c);
+      cp_async16_s(dst + 512u + d_comp, c + 4 * N);
+      cp_async16_s(dst + d_meta, f.pm + (int64_t)u * 4 * N);
+      if (lane < 16) cp_async16_s(dst + d_scale, f.ps + (int64_t)u * 2 * N);
+      cp_async16_s(dst + d_b, f.pb + u * 32);
+    }
+    cp_async_commit();
+  };
+  auto advance = [&](WsFetch& f) {     // four k-steps on
+    f.pc += (int64_t)32 * N;
+    f.pm += (int64_t)16 * N;
+    f.ps += (int64_t)8 * N;
+    f.pb += 128;
+  };
+
+  Item cur, nxt;
+  WsFetch F, NB;
+  describe(claim(), cur, F);
+  if (!F.valid) return;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) fetch(F, u);      // k-steps 0..3 of the first item
+  advance(F);
+
+  while (true) {
+    describe(claim(), nxt, NB);
+    const float gmul = g.w.g[cur.e];
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
+
+    for (int b = 0; b < nblk; ++b) {
+      if (b == nblk - 1) F = NB;     // the last block of an item prefetches the first block of the next one
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        cp_async_wait<3>();
+        __syncwarp();
+        const uint32_t st = ring + (uint32_t)u * kWsStageBytes;
+        const uint4 v0 = lds128_at(st + off_comp), v1 = lds128_at(st + off_comp + 512u);
+        const uint2 m0 = lds64_at(st + off_meta), m1 = lds64_at(st + off_meta + 128u);
+        const uint4 s0 = lds128_at(st + off_scale), s1 = lds128_at(st + off_scale + 128u);
+        const uint4 bv = lds128_at(st + d_b);
+        const uint32_t bf[4] = {bv.x, bv.y, bv.z, bv.w};
+        fetch(F, u);                 // k-step four ahead, into the slot that was just read
+        uint32_t em[4];
+        em[0] = prmt(m0.x, m1.x, 0x5140u);
+        em[1] = prmt(m0.x, m1.x, 0x7362u);
+        em[2] = prmt(m0.y, m1.y, 0x5140u);
+        em[3] = prmt(m0.y, m1.y, 0x7362u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // mma j: columns 2h, 2h+1 of the quad = bytes (2hf, 2hf+1) of word wi of every loaded vector
+          constexpr int kH[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+          const int h = kH[j];
+          const int wi = h >> 1, hf = h & 1;
+          const uint32_t c0 = word_of(v0, wi), c1 = word_of(v1, wi);
+          const __half2 sc0 = hf ? e4m3x2_to_h2<1>(word_of(s0, wi)) : e4m3x2_to_h2<0>(word_of(s0, wi));
+          const __half2 sc1 = hf ? e4m3x2_to_h2<1>(word_of(s1, wi)) : e4m3x2_to_h2<0>(word_of(s1, wi));
+          const __half2 a0 = __hmul2(hf ? e2m1x2_to_h2<2>(c0) : e2m1x2_to_h2<0>(c0), __low2half2(sc0));
+          const __half2 a1 = __hmul2(hf ? e2m1x2_to_h2<3>(c0) : e2m1x2_to_h2<1>(c0), __high2half2(sc0));
+          const __half2 a2 = __hmul2(hf ? e2m1x2_to_h2<2>(c1) : e2m1x2_to_h2<0>(c1), __low2half2(sc1));
+          const __half2 a3 = __hmul2(hf ? e2m1x2_to_h2<3>(c1) : e2m1x2_to_h2<1>(c1), __high2half2(sc1));
+          if ((j & 1) == 0)
+            mma_sp_m16n8k32<0>(acc[j], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                               *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), bf, em[j >> 1]);
+          else
+            mma_sp_m16n8k32<1>(acc[j], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                               *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), bf, em[j >> 1]);
+        }
+      }
+      advance(F);
+    }
+
+    // ---- epilogue from registers.  Column 2h + r of the quad's 16 columns for token 2t + b is acc[kJ[h]][2r + b].
+    constexpr int kJ[8] = {0, 2, 4, 6, 1, 3, 5, 7};
+    if (kSilu) {
+      const int hi = lane >> 4;                       // lanes 0..15 hold gate columns, lanes 16..31 the matching up columns
+      const int tok = 2 * t + hi;                     // each half finishes one of the quad's two tokens
+      uint32_t words[8];
+#pragma unroll
+      for (int h = 0; h < 8; ++h) {
+        float a[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float keep = hi ? acc[kJ[h]][2 * r + 1] : acc[kJ[h]][2 * r];
+          const float send = hi ? acc[kJ[h]][2 * r] : acc[kJ[h]][2 * r + 1];
+          const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
+          const float gate = (hi ? recv : keep) * gmul, up = (hi ? keep : recv) * gmul;
+          a[r] = gate / (1.0f + __expf(-gate)) * up;
+        }
+        const __half2 hv = __floats2half2_rn(a[0], a[1]);
+        words[h] = *reinterpret_cast<const uint32_t*>(&hv);
+      }
+      if (tok < cur.nt) {
+        // fragment order: word w = 8(q%2) + m of its group of 32 goes to position 4(m%4) + 2(q%2) + m/4
+        const int pair = g.plan.pairs[cur.s0 + tok];
+        __half* dst = reinterpret_cast<__half*>(g.out) + (int64_t)pair * g.ldo + (cur.grp * 2 + ((q & 3) >> 1)) * 32 + 4 * (q & 1);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) *reinterpret_cast<uint2*>(dst + 8 * m) = make_uint2(words[m], words[m + 4]);
+      }
+    } else {
+#pragma unroll
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int tok = 2 * t + b2;
+        if (tok < cur.nt) {
+          const int pair = g.plan.pairs[cur.s0 + tok];
+          const int64_t base = (int64_t)pair * g.ldo + cur.grp * 128 + q * 16;
+          float v[16];
+#pragma unroll
+          for (int h = 0; h < 8; ++h) {
+            v[2 * h] = acc[kJ[h]][b2] * gmul;
+            v[2 * h + 1] = acc[kJ[h]][2 + b2] * gmul;
+          }
+          if (g.out_dtype == B200FP4_DTYPE_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.out) + base);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (g.out_dtype == B200FP4_DTYPE_F16) {
+                const __half2 hv = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&hv);
+              } else {
+                const __nv_bfloat162 bv2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&bv2);
+              }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + base);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        }
+      }
+    }
+    if (!NB.valid) break;
+    cur = nxt;
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------------ generic
 
 // Scalar kernel for shapes the vectorised kernel does not take (N % 16 != 0, unusual scale group
@@ -1068,9 +1337,9 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int64_t max_passes(int64_t P, int64_t E) { return (P < E ? P : E) + P / kMaxTok + 1; }
 
-// plan layout: hdr[4] | pairs[P] | mapped[P] | (16-byte aligned) pass_rec[max_passes][2] int4
+// plan layout: hdr[8] | pairs[P] | mapped[P] | (16-byte aligned) pass_rec[max_passes][2] int4
 size_t plan_bytes(int64_t P, int64_t E) {
-  return align_up(sizeof(int) * (size_t)(4 + 2 * P), 16) + (size_t)max_passes(P, E) * 2 * sizeof(int4);
+  return align_up(sizeof(int) * (size_t)(8 + 2 * P), 16) + (size_t)max_passes(P, E) * 2 * sizeof(int4);
 }
 
 Plan carve_plan(void* ws, int64_t P, int64_t E) {
@@ -1078,9 +1347,9 @@ Plan carve_plan(void* ws, int64_t P, int64_t E) {
   int* base = reinterpret_cast<int*>(ws);
   Plan pl;
   pl.hdr = base;
-  pl.pairs = base + 4;
+  pl.pairs = base + 8;
   pl.mapped = pl.pairs + P;
-  pl.pass_rec = reinterpret_cast<int4*>(reinterpret_cast<unsigned char*>(ws) + align_up(sizeof(int) * (size_t)(4 + 2 * P), 16));
+  pl.pass_rec = reinterpret_cast<int4*>(reinterpret_cast<unsigned char*>(ws) + align_up(sizeof(int) * (size_t)(8 + 2 * P), 16));
   return pl;
 }
 
@@ -1216,6 +1485,52 @@ int launch_mma(const GemvArgs& g, const MmaCfg& c, int64_t grid, cudaStream_t st
   return launch_mma_t<4, 3, kSilu, 4>(g, grid, st);
 }
 
+// ---- warp-scheduled tensor-core kernel: conditions and launch
+// One scale per 16 k, K in whole blocks of four 32-wide steps, whole 128-column groups (SiLU: 64 gate + 64 up), and the
+// reference's separate [E, rows, N] tensors (the interleaved layout goes to the general kernel).
+bool ws_ok(int64_t N, int64_t K, int64_t G, int64_t inter_silu, const SparseWeights& w) {
+  if (G != K / 16 || K % 128 != 0) return false;
+  if (inter_silu > 0) {
+    if (inter_silu % 64 != 0 || N != 2 * inter_silu) return false;
+  } else if (N % 128 != 0) {
+    return false;
+  }
+  return w.comp_pair == 2 * N && w.comp_odd == N && w.meta_row == N && w.scale_row == N;
+}
+
+template <bool kSilu, int kN>
+int launch_ws_t(const GemvArgs& g, int* counter, int64_t grid, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(sparse_gemv_ws_kernel<kSilu, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kWsSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return B200FP4_STATUS_EXECUTION_FAILED;
+    }
+    attr_set[dev] = true;
+  }
+  launch_pdl(sparse_gemv_ws_kernel<kSilu, kN>, dim3((unsigned)grid), dim3(kWsThreads), kWsSmemBytes, st, g, counter);
+  return B200FP4_STATUS_SUCCESS;
+}
+
+GemvArgs make_args(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
+                   int out_dtype, int64_t ldo, int64_t N, int64_t K, int inter_silu);
+
+// A in fragment order, plan cut into passes of eight tokens, *counter zero (the plan kernel clears it).
+int run_projection_ws(const SparseWeights& w, const Plan& plan, const __half* A, int64_t lda, int a_div, void* out,
+                      int out_dtype, int64_t ldo, int64_t P, int64_t N, int64_t K, int64_t E, int inter_silu,
+                      int* counter, cudaStream_t st) {
+  GemvArgs g = make_args(w, plan, A, lda, a_div, out, out_dtype, ldo, N, K, inter_silu);
+  g.n_slabs = inter_silu > 0 ? inter_silu / 64 : (int)(N / 128);
+  int64_t grid = (max_passes(P, E) * g.n_slabs + kWsWarps - 1) / kWsWarps;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  if (grid < 1) grid = 1;
+  if (inter_silu > 0) return N == 1024 ? launch_ws_t<true, 1024>(g, counter, grid, st) : launch_ws_t<true, 0>(g, counter, grid, st);
+  return N == 2048 ? launch_ws_t<false, 2048>(g, counter, grid, st) : launch_ws_t<false, 0>(g, counter, grid, st);
+}
+
 template <bool kScale8, bool kSilu>
 int launch_gemv(const GemvArgs& g, const GemvCfg& c, int64_t grid, cudaStream_t st) {
   if (c.cg == 32) return launch_gemv_t<256, 16, 32, 2, kScale8, kSilu>(g, grid, c.smem, st);
@@ -1252,22 +1567,23 @@ int check_common(const void* A, int a_dtype, const void* out, int out_dtype, int
 }
 
 // Plan + (for bf16 activations) conversion to fp16 in one launch.
+// conv_mode: what the extra blocks do with the activation matrix a_src (kConv*); kConvNone = nothing.
 void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld, const int32_t* expert_map,
-                 int64_t global_E, int64_t E, const Plan& plan, const void* a_bf16, __half* a_f16, int64_t a_rows,
+                 int64_t global_E, int64_t E, const Plan& plan, const void* a_src, __half* a_f16, int64_t a_rows,
                  int64_t a_cols, int64_t a_ld, cudaStream_t st, int* zero_buf = nullptr, int zero_count = 0,
-                 int max_tok = kMaxTok) {
+                 int max_tok = kMaxTok, int conv_mode = kConvBf16) {
   int64_t chunks = 0;
   unsigned blocks = 1;
-  if (a_bf16 != nullptr) {
+  if (a_src == nullptr) conv_mode = kConvNone;
+  if (conv_mode != kConvNone) {
     chunks = a_rows * a_cols / 8;
     int64_t nb = (chunks + kPlanThreads - 1) / kPlanThreads;
     if (nb > 2 * (int64_t)sm_count()) nb = 2 * (int64_t)sm_count();
     blocks += (unsigned)(nb < 1 ? 1 : nb);
   }
-  moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan,
-                                                   reinterpret_cast<const __nv_bfloat16*>(a_bf16), a_f16, chunks,
+  moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan, a_src, a_f16, chunks,
                                                    (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8, zero_buf,
-                                                   zero_count, max_tok);
+                                                   zero_count, max_tok, conv_mode);
 }
 
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
@@ -1369,6 +1685,15 @@ int gemv_entry(const SparseWeights& w, int mode, const void* A, int a_dtype, con
       return B200FP4_STATUS_ALLOC_FAILED;
     Plan plan = carve_plan(workspace, P, E);
     __half* a16 = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + align_up(plan_bytes(P, E), 256));
+    if ((flags & B200FP4_SPARSE_META_ORDERED) != 0 && ws_ok(N, K, G, 0, w)) {
+      // warp-scheduled tensor-core kernel: activations copied into fragment order, eight-token passes
+      launch_plan(expert_ids, P, 1, 1, nullptr, 0, E, plan, A, a16, P, K, K, st, nullptr, 0, 8,
+                  a_bf16 ? kConvBf16Frag : kConvF16Frag);
+      zero_unmapped_rows_kernel<<<(unsigned)P, 128, 0, st>>>(plan.mapped, (int)P, out, out_dtype, N, (int)N);
+      rc = run_projection_ws(w, plan, a16, K, 1, out, out_dtype, N, P, N, K, E, 0, plan.hdr + 2, st);
+      if (rc != B200FP4_STATUS_SUCCESS) return rc;
+      return finish_launch(3);
+    }
     launch_plan(expert_ids, P, 1, 1, nullptr, 0, E, plan, a_bf16 ? A : nullptr, a16, P, K, K, st);
     zero_unmapped_rows_kernel<<<(unsigned)P, 128, 0, st>>>(plan.mapped, (int)P, out, out_dtype, N, (int)N);
     rc = run_projection(w, plan, a_bf16 ? a16 : reinterpret_cast<const __half*>(A), K, 1, out, out_dtype, N, P, N, K,
@@ -1430,7 +1755,7 @@ constexpr int64_t kStaticMaxK = 4096;
 constexpr int64_t kStaticMaxExperts = 4096;
 constexpr size_t static_align(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kStaticPlanBytes =
-    static_align(sizeof(int) * (size_t)(4 + 2 * kStaticMaxPairs), 16) +
+    static_align(sizeof(int) * (size_t)(8 + 2 * kStaticMaxPairs), 16) +
     (size_t)(kStaticMaxPairs + kStaticMaxPairs / 4 + 1) * 2 * sizeof(int4);
 constexpr size_t kStaticScratchBytes =
     static_align(kStaticPlanBytes, 256) + static_align((size_t)kStaticMaxPairs * kStaticMaxK * sizeof(__half), 256);
@@ -1592,6 +1917,24 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   off += align_up((size_t)P * H * sizeof(float), 256);
   int* done = reinterpret_cast<int*>(ws + off);
   const int64_t n_done = max_passes(P, E);
+
+  // More than 256 pairs: the warp-scheduled tensor-core kernel, one launch per projection (passes of eight tokens,
+  // activations in fragment order from the plan kernel and from the gate_up epilogue).
+  if (ordered && P > 256 && ws_ok(2 * I, H, G13, I, w13) && ws_ok(H, I, G2, 0, w2)) {
+    launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, hidden, h16, M, H, ld_h, st, done, (int)n_done, 8,
+                bf ? kConvBf16Frag : kConvF16Frag);
+    if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
+    rc = run_projection_ws(w13, plan, h16, H, (int)topk, act, B200FP4_DTYPE_F16, I, P, 2 * I, H, E, (int)I, plan.hdr + 2, st);
+    if (rc != B200FP4_STATUS_SUCCESS) return rc;
+    if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
+    rc = run_projection_ws(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, E, 0, plan.hdr + 4, st);
+    if (rc != B200FP4_STATUS_SUCCESS) return rc;
+    if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
+    dim3 gridw((unsigned)((H + 255) / 256), (unsigned)M);
+    launch_pdl(weighted_reduce_kernel, gridw, dim3(256), 0, st, (const float*)down, topk_weights, (const int*)plan.mapped,
+               out, out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
+    return finish_launch(4);
+  }
 
   // Tokens per pass: eight when the local experts see four or more tokens each on average (large
   // batches, expert parallelism with many source ranks) and both projections have a tensor-core
