@@ -26,6 +26,7 @@ SIGNATURES = {
     "b200fp4_has_hardware_acceleration": (_i32, []),
     "b200fp4_launch_count": (ctypes.c_uint64, []),
     "b200fp4_sf_swizzled_bytes": (_sz, [_i64, _i64]),
+    "b200fp4_sf_swizzle": (_i32, [_vp, _i64, _i64, _vp, _vp]),
     "b200fp4_quantize": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _vp]),
     "b200fp4_experts_quantize": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _vp]),
     "b200fp4_experts_quantize_gather": (_i32, [_vp, _i32, _i64, _i64, _vp, _vp, _vp, _i32, _i64, _vp, _i32, _vp, _vp, _vp]),
@@ -47,6 +48,8 @@ SIGNATURES = {
     "b200fp4_sparse_packed_gemv": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200fp4_convert_to_sparse_2of4": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "b200fp4_fused_moe_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200fp4_moe_router_workspace_bytes": (_sz, [_i64, _i64]),
+    "b200fp4_moe_router": (_i32, [_vp, _i64, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _sz, _vp]),
     "b200fp4_ep_record_bytes": (_sz, [_i64, _i64]),
     "b200fp4_ep_pack": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]),
     "b200fp4_fused_sparse_moe_records": (_i32, [_vp, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,

@@ -173,6 +173,16 @@ int gemm_common(Handle* h, int M, int N, int K, const void* A, const uint8_t* A_
 
 using namespace b200fp4;
 
+extern "C" int b200fp4_sf_swizzle(const void* sf_linear, int64_t rows, int64_t k_blocks, void* sf_swizzled, void* stream) {
+  if (rows < 0 || k_blocks < 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (rows == 0 || k_blocks == 0) return B200FP4_STATUS_SUCCESS;
+  if (!sf_linear || !sf_swizzled) return B200FP4_STATUS_INVALID_VALUE;
+  const int64_t KT = (k_blocks + 3) / 4, rp = (rows + 127) / 128 * 128;
+  sf_swizzle_kernel<<<blocks_for(rp * KT * 4, 256), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<const uint8_t*>(sf_linear), rows, k_blocks, rp, KT, static_cast<uint8_t*>(sf_swizzled));
+  return finish_launch(1);
+}
+
 extern "C" {
 
 B200FP4_API int cudaFP4Create(cudaFP4Handle_t* handle) {

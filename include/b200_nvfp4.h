@@ -75,6 +75,11 @@ B200FP4_API uint64_t b200fp4_launch_count(void);
  *                swizzled layout are written as zero by this call.
  * ------------------------------------------------------------------------------------------- */
 B200FP4_API size_t b200fp4_sf_swizzled_bytes(int64_t rows, int64_t k_blocks);
+/* Linear block scales [rows, k_blocks] -> the padded 128x4 tile layout (padding = 0): what a checkpoint's weight
+ * scales need once at load time.  Replaces swizzle_blockscale, vllm/model_executor/layers/quantization/utils/
+ * nvfp4_utils.py:38-51. */
+B200FP4_API int b200fp4_sf_swizzle(const void* sf_linear, int64_t rows, int64_t k_blocks, void* sf_swizzled,
+                                   void* stream);
 B200FP4_API int b200fp4_quantize(const void* x, int in_dtype, int64_t M, int64_t K, int64_t ldx,
                                  const float* global_scale, void* codes, void* sf, int sf_swizzled,
                                  void* stream);
@@ -340,6 +345,19 @@ B200FP4_API int b200fp4_grouped_gemm_nvfp4_silu_quant(
 B200FP4_API int b200fp4_moe_unpermute_reduce(const void* expert_out, int dtype, const int32_t* src2dst,
                                              const float* topk_weights, int64_t M, int64_t topk,
                                              int64_t H, void* out, void* stream);
+
+/* MoE router for decode: gate projection, softmax over the experts, top-k, renormalisation -- the step in front of
+ * the fused layer.  The reference leaves it to vLLM's torch code (its benches restate it:
+ * sparse_fp4_kernel/bench_moe_layer_e2e.py:230-236, softmax(logits).topk(k), weights / their sum); here the outputs are
+ * the device tensors b200fp4_fused_sparse_moe and b200fp4_ep_pack take, so routing never leaves the GPU.
+ *   hidden [M, H] and gate_w [E, H] of `dtype` (BF16 or F16), hidden rows ld_h elements apart; logits accumulate in f32
+ *   topk_weights [M, topk] f32 = exp(l - max) / sum over the selected experts (renormalize != 0) or over all experts
+ *   topk_ids [M, topk] i32 in decreasing order of logit; equal logits go to the lower expert id
+ *   workspace b200fp4_moe_router_workspace_bytes(M, E) bytes (the f32 logits).  topk <= 32, E <= 1024. */
+B200FP4_API size_t b200fp4_moe_router_workspace_bytes(int64_t M, int64_t E);
+B200FP4_API int b200fp4_moe_router(const void* hidden, int64_t ld_h, int dtype, const void* gate_w, int64_t M, int64_t H,
+                                   int64_t E, int64_t topk, int renormalize, float* topk_weights, int32_t* topk_ids,
+                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Expert-parallel helpers (no counterpart in the reference, which has no multi-GPU code of its

@@ -192,3 +192,92 @@ def test_reference_c_api_through_ctypes(golden_dir):
         stream.synchronize()
         assert rel_err(to_np(C2), 0.5 * (to_np(back) @ to_np(back).T)) < 1e-5
     assert L.cudaFP4Destroy(h) == 0
+
+
+def test_vllm_adapter_hook_and_closure_on_the_gpu():
+    # the weight-loading hook on a fake layer that lives on the GPU, with the CUDA converter, then the closure it installs
+    # called the way vLLM calls MarlinExperts.apply; the yardstick is the oracle over the oracle's own 2:4 conversion
+    import types
+    import synth
+    from dgx_vllm_b200 import vllm_adapter as va
+    E, I, H, M, topk = 8, 128, 256, 6, 2
+    w13 = synth.make_dense_experts(E, 2 * I, H, 41, "cpu", oracle_quantize_fn)
+    w2 = synth.make_dense_experts(E, H, I, 42, "cpu", oracle_quantize_fn)
+    P = lambda t: torch.nn.Parameter(t.cuda(), requires_grad=False)
+    layer = types.SimpleNamespace(w13_weight=P(w13["codes"]), w2_weight=P(w2["codes"]), w13_weight_scale=P(w13["sf"]),
+                                  w2_weight_scale=P(w2["sf"]), w13_weight_scale_2=P(1.0 / w13["gs"]),
+                                  w2_weight_scale_2=P(1.0 / w2["gs"]))
+    experts = types.SimpleNamespace(apply=None)
+    method = types.SimpleNamespace(moe_mk=None)
+
+    def original(m, l):
+        m.moe_mk = types.SimpleNamespace(fused_experts=experts)
+
+    assert va.process_moe_layer(method, layer, original)
+    assert layer.w13_weight.data.stride() == (0, 0, 0) and tuple(layer.w13_weight.shape) == (E, 2 * I, H // 2)
+    tw, ids = synth.make_routing(M, E, topk, 43, "cpu")
+    hidden = synth.make_hidden(M, H, 44, "cpu")
+    out = torch.zeros(M + 2, H, dtype=torch.bfloat16, device="cuda")
+    ret = experts.apply(out, hidden.cuda(), layer.w13_weight, layer.w2_weight, tw.cuda(), ids.cuda().long(), "silu", E, None,
+                        None, None, None, None, None, False)
+    assert ret is out
+
+    def sparse(w):
+        comp, meta = zip(*[oracle.sparse_2of4_pack(w["codes"][e].numpy()) for e in range(E)])
+        return np.stack(comp), np.stack(meta), np.ascontiguousarray(w["sf"].numpy().transpose(0, 2, 1)), (1.0 / w["gs"]).numpy()
+
+    ref = oracle.fused_sparse_moe(hidden.float().numpy(), tw.numpy(), ids.numpy(), None, sparse(w13), sparse(w2), I,
+                                  round_fp16=False)
+    assert rel_err(to_np(out[:M]), ref) < TOL and torch.all(out[M:] == 0)
+
+
+def test_vllm_adapter_dense_linear_and_scale_swizzle():
+    import types
+    from dgx_vllm_b200 import vllm_adapter as va
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 24, 384, 512
+    x = torch.randn(2, M // 2, K, generator=g).bfloat16()
+    w = (0.02 * torch.randn(N, K, generator=g)).bfloat16()
+    gx, gw = float(oracle.global_scale(x.float().numpy())), float(oracle.global_scale(w.float().numpy()))
+    wc, wsf = oracle.quantize_bf16(bf16_bits(w), gw)
+    swz = va.swizzle_blockscale(torch.from_numpy(wsf).cuda())
+    np.testing.assert_array_equal(to_np(swz), oracle.sf_linear_to_swizzled(wsf))
+    layer = types.SimpleNamespace(weight=torch.nn.Parameter(torch.from_numpy(wc).cuda(), requires_grad=False),
+                                  weight_scale=torch.nn.Parameter(torch.from_numpy(wsf).cuda().view(torch.float8_e4m3fn), requires_grad=False),
+                                  input_global_scale_inv=torch.tensor([gx], device="cuda"),
+                                  alpha=torch.tensor([1.0 / (np.float32(gx) * np.float32(gw))], dtype=torch.float32, device="cuda"),
+                                  output_size_per_partition=N)
+    core = va.Nvfp4LinearCore()
+    core.process_weights_after_loading(layer)
+    out = core.apply_weights(layer, x.cuda())
+    assert tuple(out.shape) == (2, M // 2, N)
+    ref = oracle.nvfp4_linear(bf16_bits(x.reshape(M, K)), gx, wc, wsf, gw)
+    assert rel_err(to_np(out).reshape(M, N), ref) < TOL
+
+
+@pytest.mark.parametrize("M,H,E,topk,dtype,renorm", [
+    (32, 2048, 512, 10, torch.bfloat16, True),       # the decode configuration's router: 2048 -> 512, top-10
+    (1, 2048, 512, 10, torch.bfloat16, True),
+    (13, 256, 72, 4, torch.float16, False),          # ragged token block, E not a multiple of 64, plain softmax weights
+    (128, 2048, 512, 10, torch.bfloat16, True),
+])
+def test_router_matches_fp32_torch(M, H, E, topk, dtype, renorm):
+    from dgx_vllm_b200.router import moe_router
+    g = torch.Generator().manual_seed(M + E)
+    hidden = torch.randn(M, H, generator=g).to(dtype)
+    gate = (torch.randn(E, H, generator=g) / H ** 0.5).to(dtype)
+    tw, ids = moe_router(hidden.cuda(), gate.cuda(), topk, renormalize=renorm)
+    logits = hidden.double() @ gate.double().t()
+    probs = torch.softmax(logits, dim=-1)
+    ref_w, ref_ids = probs.topk(topk, dim=-1)
+    if renorm:
+        ref_w = ref_w / ref_w.sum(-1, keepdim=True)
+    # ids must agree wherever the decision is not a near-tie of the fp32 accumulation (gap to the next logit > 1e-4)
+    srt = logits.sort(dim=-1, descending=True).values
+    clear = (srt[:, :topk] - srt[:, 1:topk + 1]).min(dim=-1).values > 1e-4
+    assert clear.float().mean() > 0.8
+    assert torch.equal(ids.cpu()[clear].long(), ref_ids[clear])
+    assert (tw.cpu()[clear].double() - ref_w[clear]).abs().max() < 1e-3
+    assert torch.allclose(tw.sum(-1).cpu(), torch.ones(M), atol=1e-5) or not renorm
+    # and it feeds the fused layer without a host round trip: dtypes and layouts are the ones the ops take
+    assert tw.dtype == torch.float32 and ids.dtype == torch.int32 and tw.is_contiguous() and ids.is_contiguous()
