@@ -1040,102 +1040,167 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
 // Epilogue from registers: the lane that holds 16 consecutive columns of a token writes them with 16-byte stores;
 // with SiLU the warp's 128 columns are 64 gate + the matching 64 up columns, the two halves of the warp swap one
 // token's values through shuffles, and SiLU(gate)*up leaves in fragment order for the down projection.
-constexpr int kWsThreads = 512;
-constexpr int kWsWarps = 16;
 constexpr int kWsStages = 4;
-constexpr int kWsStageBytes = 1792 + 512;
+constexpr int kWsWarps = 16;
+constexpr int kWsThreads = 32 * kWsWarps;
+constexpr int kWsStageBytes = 14 * 128 + 512;     // 8 compressed + 4 metadata + 2 scale rows of 128 bytes, B fragments of 8 tokens
 constexpr size_t kWsSmemBytes = (size_t)kWsWarps * kWsStages * kWsStageBytes + 128;
 
-struct WsFetch {
-  const uint8_t *pc, *pm, *ps;   // this lane's chunk of compressed row fr, metadata row fr, scale row fr at k-step 0
-  const __half* pb;              // this lane's B fragment at k-step 0
-  bool valid;
+// Lane-constant shared-memory offsets of the warp-scheduled kernel.
+// Stage layout: compressed rows 0..7 | metadata rows 0..3 | scale rows 0..1 (128 bytes each) | B fragments.  The 16-byte
+// chunks of a compressed row r sit at chunk ^ 2(r%4), those of a metadata row at chunk ^ 4(r/2), so that the fragment
+// loads (rows t and t+4 for lane t of a quad; metadata rows 2(t%2), 2(t%2)+1) spread over all banks.
+struct WsLane {
+  uint32_t ring;                                   // this warp's ring
+  uint32_t d_comp, d_meta, d_scale, d_b;           // where this lane's copies land (compressed rows fr and fr+4, metadata / scale row fr)
+  uint32_t off_comp, off_meta, off_scale;          // where its fragments are read from
+  int lane, q, t, fr, fc;
 };
 
-template <bool kSilu, int kN>
-__global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const GemvArgs g, int* counter) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  pdl_wait();
-  pdl_launch_dependents();
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int q = lane >> 2, t = lane & 3;
-  const int fr = lane >> 3, fc = lane & 7;
+__device__ __forceinline__ WsLane ws_lane(unsigned char* smem) {
+  WsLane L;
+  L.lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  L.q = L.lane >> 2;
+  L.t = L.lane & 3;
+  L.fr = L.lane >> 3;
+  L.fc = L.lane & 7;
+  L.ring = ((shared_addr(smem) + 127u) & ~127u) + (uint32_t)warp * (kWsStages * kWsStageBytes);
+  L.d_comp = (uint32_t)L.fr * 128u + (uint32_t)((L.fc ^ (2 * (L.fr & 3))) << 4);
+  L.d_meta = 1024u + (uint32_t)L.fr * 128u + (uint32_t)((L.fc ^ (4 * (L.fr >> 1))) << 4);
+  L.d_scale = 1536u + (uint32_t)L.fr * 128u + (uint32_t)L.fc * 16u;
+  L.d_b = 1792u + (uint32_t)L.lane * 16u;
+  L.off_comp = (uint32_t)L.t * 128u + (uint32_t)((L.q ^ (2 * L.t)) << 4);
+  L.off_meta = 1024u + (uint32_t)(2 * (L.t & 1)) * 128u + (uint32_t)((L.q ^ (4 * (L.t & 1))) << 4) + (uint32_t)(L.t >> 1) * 8u;
+  L.off_scale = 1536u + (uint32_t)L.q * 16u;
+  return L;
+}
+
+// One projection for this warp: the items [base, base + passes * groups) of the claim sequence that `counter` hands out.
+// `first` is an index this warp has already claimed; the return value is the first index it claimed that lies past
+// this projection (the caller passes it on to the next one).
+// kDep links the two projections of the MoE layer when they run in one launch: 1 = producer (done[pass] counts the
+// finished items of a pass, fenced), 2 = consumer (the B fragments of an item -- the activations the producer wrote
+// for that pass -- are fetched only once done[pass] has reached `need`), 0 = stand-alone.
+// A consumer only ever waits for items that running warps hold (an item of the first projection is claimed before any
+// item of the second), so the wait cannot deadlock; it is bounded all the same and reports through the status word.
+template <bool kSilu, int kN, int kDep>
+__device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const int base, int first, const WsLane& L,
+                                        int* done, const int need) {
+  const int lane = L.lane, q = L.q, t = L.t;
   const int N = kN ? kN : g.N;
   const int nblk = g.K >> 7;                 // blocks of four 32-wide k-steps
   const int groups = g.n_slabs;              // 128-column groups per pass
   const int n_items = g.plan.hdr[1] * groups;
-  const uint32_t ring = ((shared_addr(smem) + 127u) & ~127u) + (uint32_t)warp * (kWsStages * kWsStageBytes);
-
-  // lane-constant shared-memory offsets inside a stage: where this lane's copies land ...
-  const uint32_t d_comp = (uint32_t)fr * 128u + (uint32_t)((fc ^ (2 * (fr & 3))) << 4);
-  const uint32_t d_meta = 1024u + (uint32_t)fr * 128u + (uint32_t)((fc ^ (4 * (fr >> 1))) << 4);
-  const uint32_t d_scale = 1536u + (uint32_t)fr * 128u + (uint32_t)fc * 16u;
-  const uint32_t d_b = 1792u + (uint32_t)lane * 16u;
-  // ... and where its fragments are read from
-  const uint32_t off_comp = (uint32_t)t * 128u + (uint32_t)((q ^ (2 * t)) << 4);
-  const uint32_t off_meta = 1024u + (uint32_t)(2 * (t & 1)) * 128u + (uint32_t)((q ^ (4 * (t & 1))) << 4) + (uint32_t)(t >> 1) * 8u;
-  const uint32_t off_scale = 1536u + (uint32_t)q * 16u;
+  if (first - base >= n_items) return first;
 
   auto claim = [&]() {
     int v = 0;
     if (lane == 0) v = atomicAdd(counter, 1);
     return __shfl_sync(0xffffffffu, v, 0);
   };
-  // what the compute side needs to know about an item
+  // An item as read from its pass record: expert, group, and the pairs this lane deals with (B column q; the one or two
+  // tokens whose outputs it stores).  Pairs 0..3 sit in the record, later ones in pairs[].
   struct Item {
-    int e, nt, s0, grp;
+    int e, grp, pass, pb, ps0, ps1;
+    bool valid;
   };
-  auto describe = [&](int it, Item& d, WsFetch& f) {
-    f.valid = it < n_items;
-    if (!f.valid) return;
-    const int pass = it / groups;
-    d.grp = it - pass * groups;
-    const int4 x = g.plan.pass_rec[2 * pass], y = g.plan.pass_rec[2 * pass + 1];
+  auto pair_of = [&](const int4& x, const int4& y, int tok) {
+    if (tok >= 4) return g.plan.pairs[y.z + tok];
+    return tok == 0 ? x.z : (tok == 1 ? x.w : (tok == 2 ? y.x : y.y));
+  };
+  auto describe = [&](int claimed) {
+    Item d;
+    const int it = claimed - base;
+    d.valid = it < n_items;
+    d.e = d.grp = d.pass = d.pb = 0;
+    d.ps0 = d.ps1 = -1;
+    if (!d.valid) return d;
+    d.pass = it / groups;
+    d.grp = it - d.pass * groups;
+    const int4 x = g.plan.pass_rec[2 * d.pass], y = g.plan.pass_rec[2 * d.pass + 1];
     d.e = x.x;
-    d.nt = x.y;
-    d.s0 = y.z;
+    const int nt = x.y;
     // B column q = token q of the pass; columns past the last token repeat token 0 (their results are never stored)
-    const uint32_t pr = (uint32_t)g.plan.pairs[d.s0 + (q < d.nt ? q : 0)];
+    d.pb = pair_of(x, y, q < nt ? q : 0);
+    const int s0 = kSilu ? 2 * t + (lane >> 4) : 2 * t;
+    if (s0 < nt) d.ps0 = pair_of(x, y, s0);
+    if (!kSilu && s0 + 1 < nt) d.ps1 = pair_of(x, y, s0 + 1);
+    return d;
+  };
+  // this lane's copy sources at k-step 0 of an item
+  struct Fetch {
+    const uint8_t *pc, *pm, *ps;
+    const __half* pb;
+    bool valid;
+  };
+  auto sources = [&](const Item& d) {
+    Fetch f;
+    f.valid = d.valid;
+    f.pc = f.pm = f.ps = nullptr;
+    f.pb = nullptr;
+    if (!d.valid) return f;
+    if (kDep == 2) {
+      // the activations of this pass must be complete before any lane asks for them
+      if (lane == 0) {
+        volatile int* status = g.plan.hdr + 3;
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(done + d.pass) : "memory");
+        if (v < need && *status == 0) {
+          const long long t0 = clock64();
+          do {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(done + d.pass) : "memory");
+            if (clock64() - t0 > g.wait_cycles) {
+              *status = B200FP4_MOE_STATUS_WAIT_EXPIRED;
+              break;
+            }
+          } while (v < need);
+        }
+      }
+      __syncwarp();
+    }
+    const uint32_t pr = (uint32_t)d.pb;
     const int64_t row = g.a_magic ? (int64_t)__umulhi(pr, g.a_magic) : (int64_t)pr;
     f.pb = g.A + row * g.lda + t * 8;
     int col;
-    if (kSilu) col = fc < 4 ? d.grp * 64 + fc * 16 : g.inter + d.grp * 64 + (fc - 4) * 16;
-    else col = d.grp * 128 + fc * 16;
-    const int64_t lane_off = (int64_t)fr * N + col;
+    if (kSilu) col = L.fc < 4 ? d.grp * 64 + L.fc * 16 : g.inter + d.grp * 64 + (L.fc - 4) * 16;
+    else col = d.grp * 128 + L.fc * 16;
+    const int64_t lane_off = (int64_t)L.fr * N + col;
     f.pc = g.w.comp + ((int64_t)d.e * g.w.comp_e + lane_off);
     f.pm = g.w.meta + ((int64_t)d.e * g.w.meta_e + lane_off);
     f.ps = g.w.scale + ((int64_t)d.e * g.w.scale_e + lane_off);
+    return f;
   };
   // copies of k-step `u` (relative to f) into ring slot u; always one commit group, so that the wait counts stay fixed
-  auto fetch = [&](const WsFetch& f, int u) {
+  auto fetch = [&](const Fetch& f, int u) {
     if (f.valid) {
-      const uint32_t dst = ring + (uint32_t)u * kWsStageBytes;
+      const uint32_t dst = L.ring + (uint32_t)u * kWsStageBytes;
       const uint8_t* c = f.pc + (int64_t)u * 8 * N;
-      cp_async16_s(dst + d_comp, c);
-      cp_async16_s(dst + 512u + d_comp, c + 4 * N);
-      cp_async16_s(dst + d_meta, f.pm + (int64_t)u * 4 * N);
-      if (lane < 16) cp_async16_s(dst + d_scale, f.ps + (int64_t)u * 2 * N);
-      cp_async16_s(dst + d_b, f.pb + u * 32);
+      cp_async16_s(dst + L.d_comp, c);
+      cp_async16_s(dst + 512u + L.d_comp, c + (int64_t)4 * N);
+      cp_async16_s(dst + L.d_meta, f.pm + (int64_t)u * 4 * N);
+      if (lane < 16) cp_async16_s(dst + L.d_scale, f.ps + (int64_t)u * 2 * N);
+      cp_async16_s(dst + L.d_b, f.pb + u * 32);
     }
     cp_async_commit();
   };
-  auto advance = [&](WsFetch& f) {     // four k-steps on
+  auto advance = [&](Fetch& f) {     // four k-steps on
     f.pc += (int64_t)32 * N;
     f.pm += (int64_t)16 * N;
     f.ps += (int64_t)8 * N;
     f.pb += 128;
   };
 
-  Item cur, nxt;
-  WsFetch F, NB;
-  describe(claim(), cur, F);
-  if (!F.valid) return;
+  Item cur = describe(first);
+  Fetch F = sources(cur);
 #pragma unroll
   for (int u = 0; u < 4; ++u) fetch(F, u);      // k-steps 0..3 of the first item
   advance(F);
+  int carry;
 
   while (true) {
-    describe(claim(), nxt, NB);
+    carry = claim();
+    const Item nxt = describe(carry);
     const float gmul = g.w.g[cur.e];
     float acc[8][4];
 #pragma unroll
@@ -1144,16 +1209,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
       for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
 
     for (int b = 0; b < nblk; ++b) {
-      if (b == nblk - 1) F = NB;     // the last block of an item prefetches the first block of the next one
+      if (b == nblk - 1) F = sources(nxt);     // the last block of an item prefetches the first block of the next one
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         cp_async_wait<3>();
         __syncwarp();
-        const uint32_t st = ring + (uint32_t)u * kWsStageBytes;
-        const uint4 v0 = lds128_at(st + off_comp), v1 = lds128_at(st + off_comp + 512u);
-        const uint2 m0 = lds64_at(st + off_meta), m1 = lds64_at(st + off_meta + 128u);
-        const uint4 s0 = lds128_at(st + off_scale), s1 = lds128_at(st + off_scale + 128u);
-        const uint4 bv = lds128_at(st + d_b);
+        const uint32_t st = L.ring + (uint32_t)u * kWsStageBytes;
+        const uint4 v0 = lds128_at(st + L.off_comp), v1 = lds128_at(st + L.off_comp + 512u);
+        const uint2 m0 = lds64_at(st + L.off_meta), m1 = lds64_at(st + L.off_meta + 128u);
+        const uint4 s0 = lds128_at(st + L.off_scale), s1 = lds128_at(st + L.off_scale + 128u);
+        const uint4 bv = lds128_at(st + L.d_b);
         const uint32_t bf[4] = {bv.x, bv.y, bv.z, bv.w};
         fetch(F, u);                 // k-step four ahead, into the slot that was just read
         uint32_t em[4];
@@ -1163,7 +1228,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
         em[3] = prmt(m0.y, m1.y, 0x7362u);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          // mma j: columns 2h, 2h+1 of the quad = bytes (2hf, 2hf+1) of word wi of every loaded vector
+          // mma j takes columns 2h, 2h+1 of every quad as its rows q and q+8: bytes (2hf, 2hf+1) of word wi of the
+          // loaded vectors.  Even j: metadata from lanes t = 0, 1 (first half of the quad's columns), odd j: t = 2, 3.
           constexpr int kH[8] = {0, 4, 1, 5, 2, 6, 3, 7};
           const int h = kH[j];
           const int wi = h >> 1, hf = h & 1;
@@ -1189,13 +1255,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
     constexpr int kJ[8] = {0, 2, 4, 6, 1, 3, 5, 7};
     if (kSilu) {
       const int hi = lane >> 4;                       // lanes 0..15 hold gate columns, lanes 16..31 the matching up columns
-      const int tok = 2 * t + hi;                     // each half finishes one of the quad's two tokens
       uint32_t words[8];
 #pragma unroll
       for (int h = 0; h < 8; ++h) {
         float a[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
+          // each half of the warp finishes one of the quad's two tokens: it keeps its own value for that token and
+          // sends the other token's value to the lane that holds the matching gate / up column
           const float keep = hi ? acc[kJ[h]][2 * r + 1] : acc[kJ[h]][2 * r];
           const float send = hi ? acc[kJ[h]][2 * r] : acc[kJ[h]][2 * r + 1];
           const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
@@ -1205,20 +1272,19 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
         const __half2 hv = __floats2half2_rn(a[0], a[1]);
         words[h] = *reinterpret_cast<const uint32_t*>(&hv);
       }
-      if (tok < cur.nt) {
-        // fragment order: word w = 8(q%2) + m of its group of 32 goes to position 4(m%4) + 2(q%2) + m/4
-        const int pair = g.plan.pairs[cur.s0 + tok];
-        __half* dst = reinterpret_cast<__half*>(g.out) + (int64_t)pair * g.ldo + (cur.grp * 2 + ((q & 3) >> 1)) * 32 + 4 * (q & 1);
+      if (cur.ps0 >= 0) {
+        // fragment order: this lane's 16 gate columns are words 8(q%2) + m, m = 0..7, of the 32-column group
+        // 2 grp + (q%4)/2; word w goes to position 4(w%4) + w/4, so words m and m+4 are neighbours
+        __half* dst = reinterpret_cast<__half*>(g.out) + (int64_t)cur.ps0 * g.ldo + (cur.grp * 2 + ((q & 3) >> 1)) * 32 + 4 * (q & 1);
 #pragma unroll
         for (int m = 0; m < 4; ++m) *reinterpret_cast<uint2*>(dst + 8 * m) = make_uint2(words[m], words[m + 4]);
       }
     } else {
 #pragma unroll
       for (int b2 = 0; b2 < 2; ++b2) {
-        const int tok = 2 * t + b2;
-        if (tok < cur.nt) {
-          const int pair = g.plan.pairs[cur.s0 + tok];
-          const int64_t base = (int64_t)pair * g.ldo + cur.grp * 128 + q * 16;
+        const int pair = b2 ? cur.ps1 : cur.ps0;
+        if (pair >= 0) {
+          const int64_t o = (int64_t)pair * g.ldo + cur.grp * 128 + q * 16;
           float v[16];
 #pragma unroll
           for (int h = 0; h < 8; ++h) {
@@ -1226,7 +1292,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
             v[2 * h + 1] = acc[kJ[h]][2 + b2] * gmul;
           }
           if (g.out_dtype == B200FP4_DTYPE_F32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.out) + base);
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(g.out) + o);
 #pragma unroll
             for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
           } else {
@@ -1241,17 +1307,57 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
                 w[i] = *reinterpret_cast<const uint32_t*>(&bv2);
               }
             }
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + base);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(g.out) + o);
             dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
             dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
           }
         }
       }
     }
-    if (!NB.valid) break;
+    if (kDep == 1) {
+      // this item's activations are stored: make them visible, then count the item for its pass
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        atomicAdd(done + cur.pass, 1);
+      }
+    }
+    if (!nxt.valid) break;
     cur = nxt;
   }
   cp_async_wait<0>();
+  __syncwarp();
+  return carry;
+}
+
+template <bool kSilu, int kN>
+__global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const GemvArgs g, int* counter) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const WsLane L = ws_lane(smem);
+  int first = 0;
+  if (L.lane == 0) first = atomicAdd(counter, 1);
+  first = __shfl_sync(0xffffffffu, first, 0);
+  ws_phase<kSilu, kN, 0>(g, counter, 0, first, L, nullptr, 0);
+}
+
+// Both projections of the MoE layer in one launch: the claim sequence runs through the gate_up items and on into the
+// down items, so a warp that finds no gate_up item left starts on the down projection of passes that are complete
+// instead of idling until the slowest warp of a first launch has finished and a second launch has ramped up.
+template <int kNA, int kNB>
+__global__ void __launch_bounds__(kWsThreads, 1)
+    fused_moe_ws_kernel(const GemvArgs ga, const GemvArgs gb, int* counter, int* done, int need) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const WsLane L = ws_lane(smem);
+  int first = 0;
+  if (L.lane == 0) first = atomicAdd(counter, 1);
+  first = __shfl_sync(0xffffffffu, first, 0);
+  const int n_a = ga.plan.hdr[1] * ga.n_slabs;
+  first = ws_phase<true, kNA, 1>(ga, counter, 0, first, L, done, need);
+  ws_phase<false, kNB, 2>(gb, counter, n_a, first, L, done, need);
 }
 
 // ------------------------------------------------------------------------------------------ generic
@@ -1498,20 +1604,35 @@ bool ws_ok(int64_t N, int64_t K, int64_t G, int64_t inter_silu, const SparseWeig
   return w.comp_pair == 2 * N && w.comp_odd == N && w.meta_row == N && w.scale_row == N;
 }
 
-template <bool kSilu, int kN>
-int launch_ws_t(const GemvArgs& g, int* counter, int64_t grid, cudaStream_t st) {
-  static bool attr_set[64] = {false};
+// Opt a kernel in to the large dynamic shared memory, once per device; `attr_set` belongs to the caller, one array per
+// kernel instantiation (instantiations share their function type, so a static in here would be shared between them).
+template <typename Kernel>
+bool ws_prepare(Kernel kernel, bool* attr_set) {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(sparse_gemv_ws_kernel<kSilu, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kWsSmemBytes) != cudaSuccess) {
+  if (dev < 0 || dev >= 64) return false;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWsSmemBytes) != cudaSuccess) {
       cudaGetLastError();
-      return B200FP4_STATUS_EXECUTION_FAILED;
+      return false;
     }
     attr_set[dev] = true;
   }
-  launch_pdl(sparse_gemv_ws_kernel<kSilu, kN>, dim3((unsigned)grid), dim3(kWsThreads), kWsSmemBytes, st, g, counter);
+  return true;
+}
+
+int64_t ws_grid(int64_t max_items) {
+  int64_t grid = (max_items + kWsWarps - 1) / kWsWarps;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  return grid < 1 ? 1 : grid;
+}
+
+template <bool kSilu, int kN>
+int launch_ws_t(const GemvArgs& g, int* counter, int64_t max_items, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  if (!ws_prepare(sparse_gemv_ws_kernel<kSilu, kN>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
+  launch_pdl(sparse_gemv_ws_kernel<kSilu, kN>, dim3((unsigned)ws_grid(max_items)), dim3(kWsThreads), kWsSmemBytes, st, g,
+             counter);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -1524,11 +1645,19 @@ int run_projection_ws(const SparseWeights& w, const Plan& plan, const __half* A,
                       int* counter, cudaStream_t st) {
   GemvArgs g = make_args(w, plan, A, lda, a_div, out, out_dtype, ldo, N, K, inter_silu);
   g.n_slabs = inter_silu > 0 ? inter_silu / 64 : (int)(N / 128);
-  int64_t grid = (max_passes(P, E) * g.n_slabs + kWsWarps - 1) / kWsWarps;
-  if (grid > (int64_t)sm_count()) grid = sm_count();
-  if (grid < 1) grid = 1;
-  if (inter_silu > 0) return N == 1024 ? launch_ws_t<true, 1024>(g, counter, grid, st) : launch_ws_t<true, 0>(g, counter, grid, st);
-  return N == 2048 ? launch_ws_t<false, 2048>(g, counter, grid, st) : launch_ws_t<false, 0>(g, counter, grid, st);
+  const int64_t items = max_passes(P, E) * g.n_slabs;
+  if (inter_silu > 0) return N == 1024 ? launch_ws_t<true, 1024>(g, counter, items, st) : launch_ws_t<true, 0>(g, counter, items, st);
+  return N == 2048 ? launch_ws_t<false, 2048>(g, counter, items, st) : launch_ws_t<false, 0>(g, counter, items, st);
+}
+
+template <int kNA, int kNB>
+int launch_fused_ws_t(const GemvArgs& ga, const GemvArgs& gb, int* counter, int* done, int need, int64_t max_items,
+                      cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  if (!ws_prepare(fused_moe_ws_kernel<kNA, kNB>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
+  launch_pdl(fused_moe_ws_kernel<kNA, kNB>, dim3((unsigned)ws_grid(max_items)), dim3(kWsThreads), kWsSmemBytes, st, ga, gb,
+             counter, done, need);
+  return B200FP4_STATUS_SUCCESS;
 }
 
 template <bool kScale8, bool kSilu>
@@ -1918,22 +2047,36 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   int* done = reinterpret_cast<int*>(ws + off);
   const int64_t n_done = max_passes(P, E);
 
-  // More than 256 pairs: the warp-scheduled tensor-core kernel, one launch per projection (passes of eight tokens,
-  // activations in fragment order from the plan kernel and from the gate_up epilogue).
+  // More than 256 pairs: the warp-scheduled tensor-core kernel (passes of eight tokens, activations in fragment order
+  // from the plan kernel and from the gate_up epilogue).  Both projections share one launch and one claim sequence
+  // unless B200FP4_MOE_SEPARATE_LAUNCHES asks for one launch each.
   if (ordered && P > 256 && ws_ok(2 * I, H, G13, I, w13) && ws_ok(H, I, G2, 0, w2)) {
     launch_plan(topk_ids, P, topk, ld_ids, expert_map, global_E, E, plan, hidden, h16, M, H, ld_h, st, done, (int)n_done, 8,
                 bf ? kConvBf16Frag : kConvF16Frag);
     if (g_prof_events[0]) cudaEventRecord(g_prof_events[0], st);
-    rc = run_projection_ws(w13, plan, h16, H, (int)topk, act, B200FP4_DTYPE_F16, I, P, 2 * I, H, E, (int)I, plan.hdr + 2, st);
-    if (rc != B200FP4_STATUS_SUCCESS) return rc;
-    if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
-    rc = run_projection_ws(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, E, 0, plan.hdr + 4, st);
-    if (rc != B200FP4_STATUS_SUCCESS) return rc;
+    if (!(flags & B200FP4_MOE_SEPARATE_LAUNCHES)) {
+      GemvArgs ga = make_args(w13, plan, h16, H, (int)topk, act, B200FP4_DTYPE_F16, I, 2 * I, H, (int)I);
+      GemvArgs gb = make_args(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, H, I, 0);
+      ga.n_slabs = (int)(I / 64);
+      gb.n_slabs = (int)(H / 128);
+      const int need = ga.n_slabs + g_wait_extra_need;
+      const int64_t items = max_passes(P, E) * (ga.n_slabs + gb.n_slabs);
+      if (2 * I == 1024 && H == 2048) rc = launch_fused_ws_t<1024, 2048>(ga, gb, plan.hdr + 2, done, need, items, st);
+      else rc = launch_fused_ws_t<0, 0>(ga, gb, plan.hdr + 2, done, need, items, st);
+      if (rc != B200FP4_STATUS_SUCCESS) return rc;
+      if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
+    } else {
+      rc = run_projection_ws(w13, plan, h16, H, (int)topk, act, B200FP4_DTYPE_F16, I, P, 2 * I, H, E, (int)I, plan.hdr + 2, st);
+      if (rc != B200FP4_STATUS_SUCCESS) return rc;
+      if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
+      rc = run_projection_ws(w2, plan, act, I, 1, down, B200FP4_DTYPE_F32, H, P, H, I, E, 0, plan.hdr + 4, st);
+      if (rc != B200FP4_STATUS_SUCCESS) return rc;
+    }
     if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
     dim3 gridw((unsigned)((H + 255) / 256), (unsigned)M);
     launch_pdl(weighted_reduce_kernel, gridw, dim3(256), 0, st, (const float*)down, topk_weights, (const int*)plan.mapped,
                out, out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
-    return finish_launch(4);
+    return finish_launch((flags & B200FP4_MOE_SEPARATE_LAUNCHES) ? 4 : 3);
   }
 
   // Tokens per pass: eight when the local experts see four or more tokens each on average (large
