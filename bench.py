@@ -599,8 +599,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-mode", default="gather", choices=["gather", "a2a"],
-                    help="expert-parallel exchange: all-gather + reduce-scatter (default) or all-to-all both ways")
+    ap.add_argument("--ep-mode", default="p2p", choices=["gather", "a2a", "p2p"],
+                    help="expert-parallel exchange: this library's own dispatch / combine kernels over peer memory (default), "
+                         "NCCL all-gather + reduce-scatter, or NCCL all-to-all both ways")
     ap.add_argument("--no-parts", action="store_true", help="skip the dense GEMM / quantizer side measurements")
     ap.add_argument("--only-prefill", action="store_true",
                     help="run just the grouped prefill layer (the `moe_prefill_8192_tokens` part) and print its numbers; "

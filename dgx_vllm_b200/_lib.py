@@ -55,6 +55,10 @@ SIGNATURES = {
     "b200fp4_fused_sparse_moe_records": (_i32, [_vp, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                                 _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_ep_combine": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp]),
+    "b200fp4_ep_dispatch_p2p": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i32, _vp, _vp]),
+    "b200fp4_fused_sparse_moe_records_scatter": (_i32, [_vp, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
+                                                        _i64, _vp, _i64, _i64, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_ep_combine_p2p": (_i32, [_vp, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _i32, _vp]),
     "b200fp4_fused_moe_profile_events": (None, [_vp, _vp, _vp]),
     "b200fp4_fused_sparse_moe": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                         _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),

@@ -1410,20 +1410,33 @@ __global__ void generic_gemv_kernel(SparseWeights w, int mode, const void* A, in
   store_out(out, out_dtype, (int64_t)p * N + n, acc * w.g[e]);
 }
 
+// Where the rows of the layer's result go when they are not one [M, H] tensor: row m is row dest_row0 + m % rows_per_dest
+// of the buffer ptrs[m / rows_per_dest] (expert parallelism over peer memory: the partial rows of the tokens of rank g go
+// straight into rank g's buffer).  ptrs == nullptr: the plain tensor.
+struct OutScatter {
+  void* const* ptrs;
+  int rows_per_dest, dest_row0;
+};
+
 // out[m, h] = sum_t weight(m,t) * down[m*topk + t, h] over pairs whose expert is local.
 __global__ void weighted_reduce_kernel(const float* __restrict__ down, const float* __restrict__ topk_w,
                                        const int* __restrict__ mapped, void* out, int out_dtype, int M, int topk, int H,
-                                       int unweighted, int64_t ld_w) {
+                                       int unweighted, int64_t ld_w, OutScatter sc) {
   pdl_wait();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  const int m = blockIdx.y;
+  int m = blockIdx.y;
   if (h >= H || m >= M) return;
+  const int m_src = m;
+  if (sc.ptrs != nullptr) {
+    out = sc.ptrs[m / sc.rows_per_dest];
+    m = sc.dest_row0 + m % sc.rows_per_dest;
+  }
   float acc = 0.f;
   for (int t = 0; t < topk; ++t) {
-    const int p = m * topk + t;
+    const int p = m_src * topk + t;
     if (mapped[p] < 0) continue;
     const float v = down[(int64_t)p * H + h];
-    acc += unweighted ? v : v * topk_w[(int64_t)m * ld_w + t];
+    acc += unweighted ? v : v * topk_w[(int64_t)m_src * ld_w + t];
   }
   store_out(out, out_dtype, (int64_t)m * H + h, acc);
 }
@@ -2006,9 +2019,12 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
                           const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
                           int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
                           const float* w2_g, int64_t G2, void* out, int out_dtype, int64_t M, int64_t topk, int64_t H,
-                          int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+                          int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream,
+                          OutScatter sc = OutScatter{nullptr, 1, 0}) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return B200FP4_STATUS_INVALID_VALUE;
   if (ld_h < H || ld_w < topk || ld_ids < topk || (ld_h % 8) != 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (sc.ptrs != nullptr && (sc.rows_per_dest <= 0 || sc.dest_row0 < 0)) return B200FP4_STATUS_INVALID_VALUE;
+  if (sc.ptrs != nullptr && !out) out = workspace;      // the checks below want a non-null result pointer; it is not written
   const int64_t P = M * topk;
   int rc = check_common(hidden, h_dtype, out, out_dtype, P, 2 * I, H, G13, E);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
@@ -2075,7 +2091,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
     if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
     dim3 gridw((unsigned)((H + 255) / 256), (unsigned)M);
     launch_pdl(weighted_reduce_kernel, gridw, dim3(256), 0, st, (const float*)down, topk_weights, (const int*)plan.mapped,
-               out, out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
+               out, out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w, sc);
     return finish_launch((flags & B200FP4_MOE_SEPARATE_LAUNCHES) ? 4 : 3);
   }
 
@@ -2114,7 +2130,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
         if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
         dim3 grid1((unsigned)((H + 255) / 256), (unsigned)M);
         weighted_reduce_kernel<<<grid1, 256, 0, st>>>(down, topk_weights, plan.mapped, out, out_dtype, (int)M, (int)topk,
-                                                      (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
+                                                      (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w, sc);
         return finish_launch(3);
       }
     }
@@ -2128,7 +2144,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   if (g_prof_events[2]) cudaEventRecord(g_prof_events[2], st);
   dim3 grid((unsigned)((H + 255) / 256), (unsigned)M);
   launch_pdl(weighted_reduce_kernel, grid, dim3(256), 0, st, (const float*)down, topk_weights, (const int*)plan.mapped, out,
-             out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w);
+             out_dtype, (int)M, (int)topk, (int)H, (flags & B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT) ? 1 : 0, ld_w, sc);
   return finish_launch(4);
 }
 
@@ -2293,4 +2309,23 @@ extern "C" int b200fp4_fused_sparse_moe_records(const void* records, int64_t rec
                         global_E, w13_comp, w13_meta, w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out,
                         out_dtype, T, topk, H, I, E, flags & ~B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT, workspace, workspace_bytes,
                         stream);
+}
+
+// The same with the result scattered over several buffers: row m (token m of the T received records) goes to row
+// dest_row0 + m % rows_per_dest of the buffer out_ptrs[m / rows_per_dest].  out_ptrs is a DEVICE array of T /
+// rows_per_dest pointers, which may point into peer GPUs' memory (plain stores over NVLink).
+extern "C" int b200fp4_fused_sparse_moe_records_scatter(
+    const void* records, int64_t record_bytes, int h_dtype, const int32_t* expert_map, int64_t global_E,
+    const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g, int64_t G13,
+    const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g, int64_t G2,
+    void* const* out_ptrs, int64_t rows_per_dest, int64_t dest_row0, int out_dtype, int64_t T, int64_t topk, int64_t H, int64_t I,
+    int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!records || record_bytes != (int64_t)b200fp4_ep_record_bytes(H, topk) || !out_ptrs) return B200FP4_STATUS_INVALID_VALUE;
+  if (rows_per_dest <= 0 || rows_per_dest > 0x7FFFFFFF || dest_row0 < 0 || dest_row0 > 0x7FFFFFFF) return B200FP4_STATUS_INVALID_VALUE;
+  const unsigned char* r = reinterpret_cast<const unsigned char*>(records);
+  OutScatter sc{out_ptrs, (int)rows_per_dest, (int)dest_row0};
+  return fused_moe_impl(r, record_bytes / 2, h_dtype, reinterpret_cast<const float*>(r + H * 2 + topk * 4), record_bytes / 4,
+                        reinterpret_cast<const int32_t*>(r + H * 2), record_bytes / 4, expert_map, global_E, w13_comp, w13_meta,
+                        w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, nullptr, out_dtype, T, topk, H, I, E,
+                        flags & ~B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT, workspace, workspace_bytes, stream, sc);
 }

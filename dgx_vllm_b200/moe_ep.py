@@ -69,14 +69,16 @@ class ExpertParallelMoE:
     it, after the dispatch collective, after the local layer and after the combine (benchmark hook)."""
 
     def __init__(self, global_E: int, inter: int, w13: Optional[dict], w2: Optional[dict], group=None,
-                 local_moe_fn: Optional[Callable] = None, mode: str = "gather"):
+                 local_moe_fn: Optional[Callable] = None, mode: Optional[str] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if global_E % self.world != 0:
             raise RuntimeError("the number of experts must be divisible by the number of ranks")
-        if mode not in ("gather", "a2a"):
-            raise RuntimeError("mode must be 'gather' or 'a2a'")
+        if mode is None:     # CUDA ranks: this library's own exchange kernels; CPU stand-in ranks: collectives of the process group
+            mode = "gather" if local_moe_fn is not None else "p2p"
+        if mode not in ("gather", "a2a", "p2p"):
+            raise RuntimeError("mode must be 'gather', 'a2a' or 'p2p'")
         self.global_E = global_E
         self.inter = inter
         self.w13, self.w2 = w13, w2
@@ -87,6 +89,8 @@ class ExpertParallelMoE:
         self._bufs = {}
         self._flags = None
         self._bound = None
+        self._p2p = None
+        self._seq = 0
 
     def _cuda_local(self, hidden, topk_w, topk_ids, emap):
         if self._bound is None:       # weights are validated and their pointers bound once
@@ -196,6 +200,85 @@ class ExpertParallelMoE:
                 ev[4].record(st)
         return out
 
+    # ---- mode="p2p": dispatch and combine by this library's own kernels over peer memory (no NCCL call per step)
+    def _p2p_setup(self, dev, B, H, topk):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        G = self.world
+        R = _lib.lib().b200fp4_ep_record_bytes(H, topk)
+        align = lambda v: (v + 255) // 256 * 256
+        off_rec = 1024                                      # [0, 1024): flags [2][G] int32
+        off_parts = off_rec + align(G * B * R)
+        total = off_parts + G * B * H * 4
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)                      # every rank's flags are zero before anyone publishes one
+        base = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64)
+        self._p2p = {
+            "key": (dev.index, B, H, topk), "buf": buf, "hdl": hdl, "R": R,
+            "flag_ptrs": base.to(dev), "rec_ptrs": (base + off_rec).to(dev), "part_ptrs": (base + off_parts).to(dev),
+            "rec_local": buf.data_ptr() + off_rec, "parts_local": buf.data_ptr() + off_parts,
+            "scratch": torch.zeros(4, dtype=torch.int32, device=dev),
+        }
+        self._seq = 0
+
+    def p2p_status(self) -> int:
+        """0, or the code of the bounded wait for a peer that ran out in some step since set-up (synchronises)."""
+        return 0 if self._p2p is None else int(self._p2p["scratch"][1].item())
+
+    def _forward_p2p(self, hidden, topk_w, topk_ids, emap):
+        from . import _lib
+        from ._torch_util import dtype_code, ptr, require, stream_ptr, workspace
+        dev = hidden.device
+        B, H = hidden.shape
+        topk = topk_ids.shape[1]
+        G = self.world
+        L = _lib.lib()
+        require(hidden.is_contiguous() and hidden.dtype in (torch.bfloat16, torch.float16), "hidden must be contiguous 16-bit")
+        require(G * B * topk <= 65535, "the fused layer takes at most 65535 (token, expert) pairs: G*B*topk is larger")
+        require(not torch.cuda.is_current_stream_capturing(), "the peer-memory exchange numbers its steps on the host: not capturable")
+        ids = (topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)).contiguous()
+        tw = (topk_w if topk_w.dtype == torch.float32 else topk_w.float()).contiguous()
+        if self._p2p is None or self._p2p["key"] != (dev.index, B, H, topk):
+            self._p2p_setup(dev, B, H, topk)
+        p = self._p2p
+        T, E = G * B, self.global_E // G
+        k = ("comp_T", "meta_T", "scale_T", "g_scales")
+        ws = workspace(dev, L.b200fp4_fused_moe_workspace_bytes(T, topk, H, self.inter, E))
+        code = dtype_code(hidden.dtype)
+        if self._flags is None:
+            from .sparse_fp4_v7 import metadata_ordered
+            ok = metadata_ordered(self.w13["meta_T"]) and metadata_ordered(self.w2["meta_T"])
+            self._flags = _lib.SPARSE_META_ORDERED if ok else 0
+            self._wptrs = ([ptr(self.w13[x]) for x in k] + [self.w13["scale_T"].shape[1]] +
+                           [ptr(self.w2[x]) for x in k] + [self.w2["scale_T"].shape[1]])
+        self._seq += 1
+        out = torch.empty(B, H, dtype=hidden.dtype, device=dev)
+        ev = self.phase_events
+        st = torch.cuda.current_stream(dev)
+        with torch.cuda.device(dev):
+            if ev:
+                ev[0].record(st)
+                ev[1].record(st)
+            _lib.check(L.b200fp4_ep_dispatch_p2p(ptr(hidden), ptr(ids), ptr(tw), B, H, topk, G, self.rank, ptr(p["rec_ptrs"]),
+                                                 ptr(p["flag_ptrs"]), self._seq, ptr(p["scratch"]), st.cuda_stream), "ep_dispatch_p2p")
+            if ev:
+                ev[2].record(st)
+            _lib.check(L.b200fp4_fused_sparse_moe_records_scatter(
+                p["rec_local"], p["R"], code, ptr(emap), emap.numel(), *self._wptrs, ptr(p["part_ptrs"]), B, self.rank * B,
+                _lib.F32, T, topk, H, self.inter, E, self._flags, ptr(ws), ws.numel(), st.cuda_stream),
+                "fused_sparse_moe_records_scatter")
+            if ev:
+                ev[3].record(st)
+            _lib.check(L.b200fp4_ep_combine_p2p(p["parts_local"], B, H, G, self.rank, ptr(p["flag_ptrs"]), self._seq,
+                                                ptr(p["scratch"]), ptr(out), code, st.cuda_stream), "ep_combine_p2p")
+            if ev:
+                ev[4].record(st)
+        return out
+
     def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         emap = self.expert_map(hidden.device)
         if self.world == 1:
@@ -203,6 +286,8 @@ class ExpertParallelMoE:
             return fn(hidden, topk_w, topk_ids, emap)
         if self._fn is not None:
             return self._forward_torch(hidden, topk_w, topk_ids, emap)
+        if self.mode == "p2p":
+            return self._forward_p2p(hidden, topk_w, topk_ids, emap)
         return self._forward_cuda(hidden, topk_w, topk_ids, emap)
 
 

@@ -382,6 +382,35 @@ B200FP4_API int b200fp4_fused_sparse_moe_records(
 B200FP4_API int b200fp4_ep_combine(const void* parts, int dtype, int64_t B, int64_t H, int64_t G,
                                    void* out, void* stream);
 
+/* The same exchange without a collective library: dispatch and combine over peer memory (NVLink), initiated by the
+ * kernels themselves.  Every rank owns three buffers that all ranks can address (peer mappings; the caller allocates
+ * them, e.g. with torch's symmetric memory): records [G][B] dispatch records (slot g written by rank g), parts
+ * [G][B][H] f32 (slot g = the partial rows rank g computed for this rank's tokens), flags [2][G] i32, zero before the
+ * first step.  record_ptrs / part_ptrs / flag_ptrs are DEVICE arrays of the G ranks' pointers to those buffers; seq =
+ * 1, 2, 3, ... numbers the steps, the same on every rank; scratch = 4 ints of local device memory, zero before the first
+ * step (scratch[1] != 0 after a step: a bounded wait for a peer ran out, the step's result is not valid).
+ *   b200fp4_ep_dispatch_p2p   stores this rank's B records into slot `rank` of every rank's records buffer, publishes
+ *                             flags[0][rank] = seq on every rank, and waits (bounded, ~1 s) until all G ranks' records
+ *                             of this step have landed here
+ *   b200fp4_fused_sparse_moe_records_scatter   the fused layer over the G*B records; row m of its result goes to row
+ *                             dest_row0 + m % rows_per_dest of the buffer out_ptrs[m / rows_per_dest] (out_ptrs = part_ptrs,
+ *                             rows_per_dest = B, dest_row0 = rank * B: plain peer stores)
+ *   b200fp4_ep_combine_p2p    publishes flags[1][rank] = seq everywhere, waits for all G ranks' partial rows, adds them in
+ *                             f32: out [B, H] bf16 / f16
+ * Plain peer loads and stores only (no multicast).  Not capturable into a CUDA graph as is: seq is a launch argument. */
+B200FP4_API int b200fp4_ep_dispatch_p2p(const void* hidden, const int32_t* topk_ids, const float* topk_weights, int64_t B,
+                                        int64_t H, int64_t topk, int64_t G, int64_t rank, void* const* record_ptrs,
+                                        int32_t* const* flag_ptrs, int32_t seq, int32_t* scratch, void* stream);
+B200FP4_API int b200fp4_fused_sparse_moe_records_scatter(
+    const void* records, int64_t record_bytes, int h_dtype, const int32_t* expert_map, int64_t global_E,
+    const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g, int64_t G13,
+    const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g, int64_t G2,
+    void* const* out_ptrs, int64_t rows_per_dest, int64_t dest_row0, int out_dtype, int64_t T, int64_t topk, int64_t H,
+    int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream);
+B200FP4_API int b200fp4_ep_combine_p2p(const float* parts, int64_t B, int64_t H, int64_t G, int64_t rank,
+                                       int32_t* const* flag_ptrs, int32_t seq, int32_t* scratch, void* out, int out_dtype,
+                                       void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * The reference's declared C API, exported under its own names so that a program written against
  * cutlass_nvfp4/cuda_fp4_gemm.h links against this library unchanged (the reference declares these
