@@ -38,6 +38,8 @@ struct GemmParams {
   void* out;
   int out_bf16;
   int out_f32;          // dense mode only: out is fp32 [M, N] (the accumulator times alpha, unrounded)
+  int out_tma;          // dense 16-bit output through map_out: the epilogue stages tiles in shared memory and the copy
+                        // engine writes whole lines (256-wide tiles only)
   int M, N, K;
   int m_tiles, n_tiles, k_stages;
   int* status;          // 0 = ok; otherwise the code of the wait that expired
@@ -147,7 +149,7 @@ __device__ __forceinline__ void silu_quant_row(const uint32_t* pg, const uint32_
 
 // BN = tile width; KB = 64-wide k-blocks (MMAs) per shared-memory stage.  Smaller stages do not change
 // the bytes resident in shared memory but refill in finer steps, which keeps more of them in flight.
-template <int BN, int KB>
+template <int BN, int KB, bool kOutTma = false>
 struct Cfg {
   static constexpr int kAcc = BN == 128 ? 2 : 1;                    // accumulator buffers in tensor memory
   static constexpr int kSfTiles = BN / 128;                         // 128-row scale tiles on the B side
@@ -157,14 +159,16 @@ struct Cfg {
   static constexpr int kStageSFA = KB * 512;
   static constexpr int kStageSFB = kSfTiles * KB * 512;
   static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
-  static constexpr int kStages = (BN == 128 ? 24 : 16) / KB;
+  // BN = 256 gives one of its four stages to the epilogue's staging buffers (tile stores through the copy engine)
+  static constexpr int kStages = (BN == 128 ? 24 : (kOutTma ? 12 : 16)) / KB;
+  static constexpr int kOutStage = kOutTma ? 8 * 4096 : 0;         // 8 epilogue warps x [32 rows x 64 columns] 16-bit
   // tensor-memory column map: accumulators, then one scale-factor block per shared-memory stage
   // (4 columns per k-block for A, 4*kSfTiles for B)
   static constexpr uint32_t kSfCols = KB * (4 + 4 * kSfTiles);
   static constexpr uint32_t kSfBase = kAcc * BN;
   static_assert(kSfBase + kStages * kSfCols <= 512, "tensor memory budget");
   static constexpr int kBarBytes = 1024;
-  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + kBarBytes;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + kOutStage + 1024 /*alignment slack*/ + kBarBytes;
   // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major A and B, N = BN, M = 128, dense K = 64
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 };
@@ -172,12 +176,14 @@ struct Cfg {
 template <int BN, int KB, bool kGrouped, bool kSiluQuant = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const GemmParams p) {
-  using C = Cfg<BN, KB>;
+                      const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+  constexpr bool kOutTma = BN == 256 && !kGrouped && !kSiluQuant;     // the dense wide-tile kernel stores tiles through the copy engine
+  using C = Cfg<BN, KB, kOutTma>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::kStages * C::kStageBytes);
+  unsigned char* out_stage = smem + (size_t)C::kStages * C::kStageBytes;      // 1024-byte aligned (stages are multiples of 1 KiB)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + C::kOutStage);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + C::kStages;
   uint64_t* acc_full = bars + 2 * C::kStages;
@@ -438,6 +444,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      if (kOutTma && p.out_tma) {
+        // This warp's 32 rows x 128 columns leave in two halves of 64 columns (128 bytes per row): rows go to a private
+        // staging buffer with the 128-byte swizzle of the tensor map (16-byte chunk c of row r at c ^ (r % 8): the
+        // lanes of a warp write different banks), one lane hands the box to the copy engine, which writes whole lines
+        // and clips rows / columns beyond the tensor.
+        const uint32_t stg = smem_u32(out_stage) + (uint32_t)((warp >= 10 ? 4 : 0) + quarter) * 4096u;
+        const int row0 = ti.a_row0 + quarter * 32;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          if (lane == 0) bulk_wait_read0();          // the previous box has left the buffer
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            sts128(stg + (uint32_t)lane * 128u + (uint32_t)((c ^ (lane & 7)) << 4), packed[hh * 32 + 4 * c],
+                   packed[hh * 32 + 4 * c + 1], packed[hh * 32 + 4 * c + 2], packed[hh * 32 + 4 * c + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int col0 = ti.n0 + (c_first * 32) + hh * 64;
+          if (lane == 0 && col0 < p.N && row0 < p.M) {
+            tma_store_2d(&map_out, col0, row0, stg);
+            bulk_commit();
+          }
+        }
+        continue;
+      }
       if (row < ti.row_end) {
         uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N;
 #pragma unroll
@@ -467,6 +498,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
   // all roles fall through to here (also after a timed-out wait), so tensor memory is always freed
+  if (kOutTma && p.out_tma && lane == 0 && (warp >= 2 && (warp < 6 || warp >= 10))) bulk_wait0();
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -783,14 +815,34 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_by
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [rows, cols] 16-bit row-major output; box = 64 columns (128 bytes) x 32 rows, 128-byte swizzle
+bool make_out_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int KB, bool kGrouped, bool kSiluQuant = false>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int max_m_tiles, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int max_m_tiles, cudaStream_t st,
+                const CUtensorMap* mo = nullptr) {
+  using C = Cfg<BN, KB, BN == 256 && !kGrouped && !kSiluQuant>;
+  CUtensorMap dummy = {};
+  if (mo == nullptr) {
+    mo = &dummy;
+    p.out_tma = 0;
+  }
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(nvfp4_gemm_kernel<BN, KB, kGrouped, kSiluQuant>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Cfg<BN, KB>::kSmemBytes) != cudaSuccess) {
+                             (int)C::kSmemBytes) != cudaSuccess) {
       cudaGetLastError();
       return B200FP4_STATUS_EXECUTION_FAILED;
     }
@@ -801,7 +853,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, int 
   if (grid > sm_count()) grid = sm_count();
   if (grid < 1) grid = 1;
   p.k_stages = (p.K + KB * 64 - 1) / (KB * 64);
-  nvfp4_gemm_kernel<BN, KB, kGrouped, kSiluQuant><<<(unsigned)grid, kGemmThreads, Cfg<BN, KB>::kSmemBytes, st>>>(ma, mb, p);
+  nvfp4_gemm_kernel<BN, KB, kGrouped, kSiluQuant><<<(unsigned)grid, kGemmThreads, C::kSmemBytes, st>>>(ma, mb, *mo, p);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -812,9 +864,9 @@ int stage_kblocks() { return 4; }
 
 template <bool kGrouped>
 int dispatch_gemm(int bn, int kb, const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_m_tiles,
-                  cudaStream_t st) {
+                  cudaStream_t st, const CUtensorMap* mo = nullptr) {
   (void)kb;
-  if (bn == 256) return launch_gemm<256, 4, kGrouped>(ma, mb, p, max_m_tiles, st);
+  if (bn == 256) return launch_gemm<256, 4, kGrouped>(ma, mb, p, max_m_tiles, st, mo);
   return launch_gemm<128, 4, kGrouped>(ma, mb, p, max_m_tiles, st);
 }
 
@@ -871,7 +923,11 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   p.g_mtiles = nullptr;
   p.g_alphas = nullptr;
   p.g_sfb_expert_bytes = 0;
-  int rc = dispatch_gemm<false>(bn, kb, ma, mb, p, p.m_tiles, st);
+  // wide tiles, 16-bit output with 16-byte aligned rows: tiles leave through the copy engine
+  CUtensorMap mo;
+  const bool tma_out = bn == 256 && !p.out_f32 && (N % 8) == 0 && make_out_map(&mo, out, (uint64_t)M, (uint64_t)N);
+  p.out_tma = tma_out ? 1 : 0;
+  int rc = dispatch_gemm<false>(bn, kb, ma, mb, p, p.m_tiles, st, tma_out ? &mo : nullptr);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
   return finish_launch(2);
 }
@@ -915,6 +971,7 @@ static int grouped_gemm_impl(const void* a_codes, const void* b_codes, const voi
   p.out = out;
   p.out_bf16 = out_dtype == B200FP4_DTYPE_BF16;
   p.out_f32 = 0;
+  p.out_tma = 0;
   p.M = (int)rows_capacity; p.N = (int)N; p.K = (int)K;
   p.m_tiles = max_tiles;
   p.status = reinterpret_cast<int*>(workspace);
