@@ -483,6 +483,89 @@ def bench_decode_stack(dev, batches=(1, 32, 128), layers: int = 48, distinct_lay
     return out
 
 
+def bench_decode_stack_ep(dev, world: int, rank: int, ep_mode: str, batches=(1, 32, 128), layers: int = 48,
+                          distinct_layers: int = 4, reps: int = 5):
+    """BASELINE configs[4] on G GPUs: the 48-layer stack with the routed experts expert-parallel (512/G per GPU, the same
+    exchange as the headline layer) and the shared dense NVFP4 expert replicated; every GPU brings its own batch.  Eager
+    launches (the peer-memory exchange numbers its steps on the host).  Device time per token step, max over ranks; the last
+    layer's routed output on rank 0's first tokens is checked against the CPU oracle (each rank evaluates its own experts,
+    one all-reduce adds the partial rows)."""
+    import torch
+    import torch.distributed as dist
+    import synth
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant
+    from dgx_vllm_b200 import grouped_moe as gm
+    from dgx_vllm_b200.moe_ep import ExpertParallelMoE
+
+    E, H, I, topk = E_TOTAL, HIDDEN, INTER, TOPK
+    El = E // world
+
+    def qfn(w, gs):
+        c, s_ = scaled_fp4_quant(w, gs, is_sf_swizzled_layout=False)
+        return c, s_.view(torch.uint8)
+
+    sets = []
+    gen = torch.Generator(device=dev).manual_seed(99)           # shared expert: the same on every rank
+    for li in range(distinct_layers):
+        w13 = synth.make_sparse_experts(El, 2 * I, H, 3000 + 10 * li + rank, dev, qfn)
+        w2 = synth.make_sparse_experts(El, H, I, 4000 + 10 * li + rank, dev, qfn)
+        sh = []
+        for (N, K) in ((2 * I, H), (H, I)):
+            w = (0.02 * torch.randn(N, K, generator=gen, device=dev)).to(torch.bfloat16)
+            g = synth.global_scale_of(w)
+            c, s_ = scaled_fp4_quant(w, g)
+            sh.append((c, s_, g))
+        sets.append((ExpertParallelMoE(E, I, w13, w2, mode=ep_mode), w13, w2, sh))
+    out = {}
+    for B in batches:
+        xs = [synth.make_hidden(B, H, 500 + l + 100 * rank, dev) for l in range(layers)]
+        routes = [synth.make_routing(B, E, topk, 700 + l + 100 * rank, dev) for l in range(layers)]
+        gx = torch.tensor([448.0 * 6.0 / 6.0], dtype=torch.float32, device=dev)
+        ga = torch.tensor([448.0 * 6.0 / 4.0], dtype=torch.float32, device=dev)
+        offs = torch.tensor([0, B], dtype=torch.int32, device=dev)
+        bso = torch.tensor([0, (B + 127) // 128 * 128], dtype=torch.int32, device=dev)
+        alphas = [((1.0 / (gx * sh[0][2])).float(), (1.0 / (ga * sh[1][2])).float()) for (_, _, _, sh) in sets]
+
+        def stack():
+            acc = y = None
+            for l in range(layers):
+                layer, _, _, sh = sets[l % distinct_layers]
+                x = xs[l]
+                tw, ids = routes[l]
+                y = layer.forward(x, tw, ids)
+                (c13, s13, _), (c2, s2, _) = sh
+                xc, xsf = scaled_fp4_quant(x, gx)
+                al13, al2 = alphas[l % distinct_layers]
+                gu = cutlass_scaled_fp4_mm(xc, c13, xsf, s13, al13, torch.bfloat16)
+                hc, hsf = gm.silu_and_mul_scaled_fp4_experts_quant(gu, ga, offs, bso)
+                z = cutlass_scaled_fp4_mm(hc, c2, hsf, s2, al2, torch.bfloat16)
+                acc = y + z if acc is None else acc + y + z
+            return acc, y
+
+        for _ in range(2):
+            stack()
+        ts = []
+        for _ in range(reps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            res, y_last = stack()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        t = torch.tensor([statistics.mean(ts)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t = float(t.item())
+        layer, w13, w2, _ = sets[(layers - 1) % distinct_layers]
+        ver = verify_layer_step(layer, (xs[-1], routes[-1][0], routes[-1][1]), w13, w2, world, rank, dev, n_tok=min(2, B))
+        out[f"batch_{B}_per_gpu"] = {"tokens_per_s": B * world / t, "ms_per_token_step": t * 1e3, "us_per_layer": t / layers * 1e6,
+                                     "finite": bool(torch.isfinite(res.float()).all().item()), "verified_last_layer": ver}
+    out["config"] = (f"{layers} layers, {distinct_layers} distinct weight sets cycled, routed 2:4 sparse experts expert-parallel over "
+                     f"{world} GPUs ({El} per GPU, exchange: {ep_mode}) + replicated shared dense NVFP4 expert; eager launches")
+    return out
+
+
 def _rel(got, ref):
     import numpy as np
     return float(np.max(np.abs(np.asarray(got, np.float64) - np.asarray(ref, np.float64))) / (np.max(np.abs(ref)) + 1e-30))
@@ -660,6 +743,18 @@ def main():
     for i in range(args.warmup):
         step(i)
     barrier()
+    ep_mode_used = args.ep_mode if world > 1 else None
+    if world > 1 and args.ep_mode == "p2p":
+        # the peer-memory exchange reports a bounded wait that ran out through a status word: if any rank saw one during
+        # the warm-up, every rank switches to the NCCL exchange for the rest of the run and the line says so
+        stt = torch.tensor([layer.p2p_status()], dtype=torch.int32, device=dev)
+        dist.all_reduce(stt, op=dist.ReduceOp.MAX)
+        if int(stt.item()) != 0:
+            layer = ExpertParallelMoE(E_TOTAL, INTER, w13, w2, mode="gather")
+            ep_mode_used = f"gather (the peer-memory exchange reported status {int(stt.item())} during warm-up)"
+            for i in range(args.warmup):
+                step(i)
+            barrier()
     verified = verify_layer_step(layer, batches[0], w13, w2, world, rank, dev)
     barrier()
 
@@ -760,7 +855,7 @@ def main():
                           dtype=torch.float64, device=dev).mean(0)
         dist.all_reduce(ph, op=dist.ReduceOp.MAX)
         ep_phases = dict(zip(("pack_us", "dispatch_us", "local_layer_us", "combine_us"), [float(x) for x in ph.tolist()]))
-        ep_phases["mode"] = args.ep_mode
+        ep_phases["mode"] = ep_mode_used
 
     # ---- e2e: host buffers in, host result out, through the public op
     host = []
@@ -794,6 +889,8 @@ def main():
         nshard_parts = bench_dense_nshard(dev, flush, world, rank)
         torch.cuda.empty_cache()
         nshard_parts[f"moe_prefill_8192_tokens_ep{world}"] = bench_moe_prefill_ep(dev, flush, world, rank)
+        torch.cuda.empty_cache()
+        nshard_parts[f"decode_stack_48_layers_ep{world}"] = bench_decode_stack_ep(dev, world, rank, "gather" if str(ep_mode_used).startswith("gather") else args.ep_mode)
     h2d = B * HIDDEN * 2 + B * TOPK * 8
     d2h = B * HIDDEN * 2
 
@@ -806,6 +903,8 @@ def main():
                 "gpu_launches": launches, "clocks": clocks, "verified": verified}
         if ep_phases:
             line["ep_phases"] = ep_phases
+        if ep_mode_used:
+            line["config"]["ep_exchange"] = ep_mode_used
         ref_gpu = None
         if world == 1 and not args.no_parts:
             ref_gpu = bench_reference_v7_gpu(dev, w13, w2, batches, flush, layer.forward)
