@@ -39,8 +39,8 @@ BYTES_PER_EXPERT_DOWN = HIDDEN * INTER * 7 // 16
 N_ROUTINGS = 8
 # dram__bytes_read.sum + dram__bytes_write.sum of the gate_up and down GEMV launches of one layer, per routed expert,
 # from the ncu capture whose summary is committed with the profiles (244 routed experts: 233.61 MB + 118.83 MB)
-NCU_TRAFFIC_BYTES_PER_EXPERT = (233.61e6 + 118.83e6) / 244.0
-NCU_TRAFFIC_SOURCE = "ncu capture of the two GEMV launches (batch 32, 244 routed experts), scaled by routed experts"
+NCU_TRAFFIC_BYTES_PER_EXPERT = (325.34e6 + 4.65e6) / 244.0
+NCU_TRAFFIC_SOURCE = "ncu capture of the one-launch GEMV kernel (batch 32, 244 routed experts), scaled by routed experts"
 
 
 def measured_peaks():
@@ -839,7 +839,7 @@ def main():
     roofline = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
                 "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE if world == 1 else None,
                 "peak_kind": f"{peak_kind} copy bandwidth",
-                "kernel": "sparse_gemv_mma_kernel: gate_up+SiLU and down projections of one layer (tensor-core 2:4 GEMV)",
+                "kernel": "fused_moe_ws_kernel: gate_up+SiLU and down projections of one layer in one launch (tensor-core 2:4 GEMV)",
                 "per_launch_us": {"both_projections": statistics.mean(t_both) * 1e6},
                 "algorithmic_bytes_per_step": (sum(b_gu) + sum(b_dn)) / args.steps,
                 "unique_experts_mean": statistics.mean(uniq), "local_pairs_mean": statistics.mean(local_pairs)}

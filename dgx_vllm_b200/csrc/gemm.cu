@@ -19,6 +19,8 @@
 //     the global stores, so only the ~1200-cycle drain is exposed; it moves 25 % fewer bytes per flop.
 // Every mbarrier wait is bounded: on expiry the kernel records an error code in the status word
 // and all roles drain out, so a protocol error cannot hang the GPU.
+#include <cstring>
+#include <mutex>
 #include <type_traits>
 
 #include "sm100_ptx.cuh"
@@ -193,6 +195,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(sf_full + C::kStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // dense mode: the status word is cleared here instead of by a separate memset (a wait only writes it after its ~1 s
+  // budget, long after this store); in grouped mode the tile-list kernel has cleared it
+  if (!kGrouped && blockIdx.x == 0 && threadIdx.x == 0) *p.status = 0;
   const int m_tiles = kGrouped ? p.g_hdr[0] : p.m_tiles;
   const int n_tiles_total = m_tiles * p.n_tiles;
 
@@ -800,8 +805,43 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoded maps are remembered by their arguments (a weight is encoded once, not once per call).
+struct MapKey {
+  const void* base;
+  uint64_t rows, row_bytes;
+  uint32_t box_rows;
+  int box_bytes;
+};
+struct MapCache {
+  static constexpr int kSlots = 64;
+  MapKey key[kSlots];
+  CUtensorMap map[kSlots];
+  bool used[kSlots] = {false};
+  std::mutex mu;
+};
+MapCache g_map_cache;
+
+bool make_map_uncached(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, int box_bytes);
+
 // [rows, row_bytes] u8 row-major; box = box_bytes (128/64/32) x box_rows with the matching swizzle, zero fill out of bounds
 bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, int box_bytes) {
+  const MapKey k{base, rows, row_bytes, box_rows, box_bytes};
+  const size_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + rows * 31 + box_rows;
+  const int slot = (int)(h % MapCache::kSlots);
+  std::lock_guard<std::mutex> lock(g_map_cache.mu);
+  if (g_map_cache.used[slot] && memcmp(&g_map_cache.key[slot], &k, sizeof(MapKey)) == 0) {
+    *map = g_map_cache.map[slot];
+    return true;
+  }
+  if (!make_map_uncached(map, base, rows, row_bytes, box_rows, box_bytes)) return false;
+  memset(&g_map_cache.key[slot], 0, sizeof(MapKey));
+  g_map_cache.key[slot] = k;
+  g_map_cache.map[slot] = *map;
+  g_map_cache.used[slot] = true;
+  return true;
+}
+
+bool make_map_uncached(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, int box_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {row_bytes, rows};
@@ -911,10 +951,6 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   int bn = tile_n;
   if (bn == 0) bn = (p.m_tiles * ((N + 255) / 256) >= sm_count()) ? 256 : 128;
   const int kb = stage_kblocks();
-  if (cudaMemsetAsync(workspace, 0, 16, st) != cudaSuccess) {
-    cudaGetLastError();
-    return B200FP4_STATUS_EXECUTION_FAILED;
-  }
   CUtensorMap ma, mb;
   if (!make_map(&ma, a_codes, (uint64_t)M, (uint64_t)K / 2, kBM, kb * 32) ||
       !make_map(&mb, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn, kb * 32))
@@ -929,7 +965,7 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   p.out_tma = tma_out ? 1 : 0;
   int rc = dispatch_gemm<false>(bn, kb, ma, mb, p, p.m_tiles, st, tma_out ? &mo : nullptr);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
-  return finish_launch(2);
+  return finish_launch(1);
 }
 
 // ---------------------------------------------------------------------------------------- grouped entry points

@@ -58,6 +58,11 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         assert np.max(np.abs(got - ref)) <= TOL * np.max(np.abs(ref))
         ids = case[5].cpu().numpy()
         assert np.all(got[ids < 0] == 0)
+        # and against the CPU oracle of the reference's batched_sparse_v7 (same tolerance as the other GEMV parity tests)
+        import oracle
+        A, comp, meta, scale, g = (t.cpu() for t in case[:5])
+        want = oracle.batched_sparse_gemv(A.float().numpy(), comp.numpy(), meta.numpy(), scale.numpy(), g.numpy(), ids)
+        assert np.max(np.abs(got - want)) <= TOL * np.max(np.abs(want))
 
 
 def test_static_scratch_entry_rejects_sizes_beyond_its_fixed_scratch():
