@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libb200nvfp4.so")
 
 F16, BF16, F32 = 0, 1, 2
-MOE_ROUTER_WEIGHT_ON_INPUT, SPARSE_META_ORDERED, MOE_SEPARATE_LAUNCHES = 1, 2, 4     # flags of the sparse entry points
+MOE_ROUTER_WEIGHT_ON_INPUT, SPARSE_META_ORDERED, MOE_SEPARATE_LAUNCHES, MOE_HOST_DIRECT_OUT = 1, 2, 4, 8     # flags of the sparse entry points
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -80,6 +80,9 @@ SIGNATURES = {
     "b200fp4_fused_moe_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "b200fp4_fused_sparse_moe_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                              _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_fused_sparse_moe_host_async": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp,
+                                                   _vp, _i64, _vp, _i32, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz,
+                                                   _vp, _vp]),
 }
 
 _lib = None

@@ -21,6 +21,8 @@
 //     gate_up epilogue; the router-weighted sum is a small deterministic kernel (no atomics).
 #include <type_traits>
 
+#include <mutex>
+
 #include "common.cuh"
 
 extern "C" size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E);
@@ -1416,6 +1418,9 @@ __global__ void generic_gemv_kernel(SparseWeights w, int mode, const void* A, in
 struct OutScatter {
   void* const* ptrs;
   int rows_per_dest, dest_row0;
+  // the layer's status word, forwarded by its last kernel (status_out may be host memory the device can address)
+  int* status_out = nullptr;
+  const int* status_src = nullptr;
 };
 
 // out[m, h] = sum_t weight(m,t) * down[m*topk + t, h] over pairs whose expert is local.
@@ -1425,6 +1430,7 @@ __global__ void weighted_reduce_kernel(const float* __restrict__ down, const flo
   pdl_wait();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   int m = blockIdx.y;
+  if (sc.status_out != nullptr && h == 0 && m == 0) *sc.status_out = *sc.status_src;
   if (h >= H || m >= M) return;
   const int m_src = m;
   if (sc.ptrs != nullptr) {
@@ -2051,6 +2057,7 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
   Plan plan = carve_plan(ws, P, E);
+  sc.status_src = plan.hdr + 3;
   size_t off = align_up(plan_bytes(P, E), 256);
   __half* h16 = reinterpret_cast<__half*>(ws + off);
   off += align_up((size_t)M * H * sizeof(__half), 256);
@@ -2172,14 +2179,52 @@ extern "C" size_t b200fp4_fused_moe_host_workspace_bytes(int64_t M, int64_t topk
   return host_stage_bytes(M, topk, H) + b200fp4_fused_moe_workspace_bytes(M, topk, H, I, E);
 }
 
-extern "C" int b200fp4_fused_sparse_moe_host(const void* hidden_host, int h_dtype, const float* topk_weights_host,
-                                             const int32_t* topk_ids_host, const int32_t* expert_map, int64_t global_E,
-                                             const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
-                                             const float* w13_g, int64_t G13, const uint8_t* w2_comp,
-                                             const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g,
-                                             int64_t G2, void* out_host, int out_dtype, int64_t M, int64_t topk,
-                                             int64_t H, int64_t I, int64_t E, int flags, void* workspace,
-                                             size_t workspace_bytes, void* stream) {
+namespace {
+// Events that order a copy stream against the compute stream, one pair per workspace (the staging buffers they guard
+// live in the workspace).  Created on first use, kept for the life of the process.
+struct HostSlotEvents {
+  const void* workspace;
+  int device;
+  cudaEvent_t loaded, consumed;
+  bool used;
+};
+constexpr int kHostSlots = 32;
+HostSlotEvents g_host_slots[kHostSlots];
+int g_host_slot_count = 0;
+std::mutex g_host_slot_mutex;
+
+HostSlotEvents* host_slot_events(const void* workspace) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(g_host_slot_mutex);
+  for (int i = 0; i < g_host_slot_count; ++i)
+    if (g_host_slots[i].workspace == workspace && g_host_slots[i].device == dev) return &g_host_slots[i];
+  if (g_host_slot_count == kHostSlots) return nullptr;
+  HostSlotEvents& e = g_host_slots[g_host_slot_count];
+  if (cudaEventCreateWithFlags(&e.loaded, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  if (cudaEventCreateWithFlags(&e.consumed, cudaEventDisableTiming) != cudaSuccess) {
+    cudaEventDestroy(e.loaded);
+    return nullptr;
+  }
+  e.workspace = workspace;
+  e.device = dev;
+  e.used = false;
+  ++g_host_slot_count;
+  return &e;
+}
+}  // namespace
+
+// Enqueue-only form: copies in (on copy_stream when one is given, ordered against the layer by events), the layer, the
+// copies out; no host synchronisation.
+extern "C" int b200fp4_fused_sparse_moe_host_async(const void* hidden_host, int h_dtype, const float* topk_weights_host,
+                                                   const int32_t* topk_ids_host, const int32_t* expert_map,
+                                                   int64_t global_E, const uint8_t* w13_comp, const uint8_t* w13_meta,
+                                                   const uint8_t* w13_scale, const float* w13_g, int64_t G13,
+                                                   const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
+                                                   const float* w2_g, int64_t G2, void* out_host, int out_dtype,
+                                                   int32_t* status_host, int64_t M, int64_t topk, int64_t H, int64_t I,
+                                                   int64_t E, int flags, void* workspace, size_t workspace_bytes,
+                                                   void* stream, void* copy_stream) {
   if (M < 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0) return B200FP4_STATUS_INVALID_VALUE;
   if (M == 0) return B200FP4_STATUS_SUCCESS;
   if (!hidden_host || !topk_weights_host || !topk_ids_host || !out_host || !workspace)
@@ -2193,22 +2238,82 @@ extern "C" int b200fp4_fused_sparse_moe_host(const void* hidden_host, int h_dtyp
   char* d_w = d_out + align_up(nh, 256);
   char* d_ids = d_w + align_up(nr, 256);
   cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemcpyAsync(d_ids, topk_ids_host, nr, cudaMemcpyHostToDevice, st) != cudaSuccess ||
-      cudaMemcpyAsync(d_w, topk_weights_host, nr, cudaMemcpyHostToDevice, st) != cudaSuccess ||
-      cudaMemcpyAsync(d_hidden, hidden_host, nh, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+  cudaStream_t cs = copy_stream ? (cudaStream_t)copy_stream : st;
+  HostSlotEvents* ev = nullptr;
+  if (cs != st) {
+    ev = host_slot_events(workspace);
+    if (!ev) return B200FP4_STATUS_ALLOC_FAILED;
+    // the staging buffers may still be read by the layer of the previous submission with this workspace
+    if (ev->used && cudaStreamWaitEvent(cs, ev->consumed, 0) != cudaSuccess) {
+      cudaGetLastError();
+      return B200FP4_STATUS_EXECUTION_FAILED;
+    }
+  }
+  if (cudaMemcpyAsync(d_ids, topk_ids_host, nr, cudaMemcpyHostToDevice, cs) != cudaSuccess ||
+      cudaMemcpyAsync(d_w, topk_weights_host, nr, cudaMemcpyHostToDevice, cs) != cudaSuccess ||
+      cudaMemcpyAsync(d_hidden, hidden_host, nh, cudaMemcpyHostToDevice, cs) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
   }
+  if (ev && (cudaEventRecord(ev->loaded, cs) != cudaSuccess || cudaStreamWaitEvent(st, ev->loaded, 0) != cudaSuccess)) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  // result rows and status word: into the staging buffer and copied out, or -- with B200FP4_MOE_HOST_DIRECT_OUT and
+  // pinned memory the device can address -- stored by the layer's last kernel straight into the caller's buffers
+  auto mapped_of = [](void* host) -> void* {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+  };
+  void* out_target = d_out;
+  OutScatter sc{nullptr, 1, 0};
+  if (flags & B200FP4_MOE_HOST_DIRECT_OUT) {
+    if (void* mapped = mapped_of(out_host)) out_target = mapped;
+    if (status_host) sc.status_out = static_cast<int*>(mapped_of(status_host));
+  }
   const int rc = fused_moe_impl(d_hidden, H, h_dtype, reinterpret_cast<const float*>(d_w), topk,
                                 reinterpret_cast<const int32_t*>(d_ids), topk, expert_map, global_E, w13_comp, w13_meta,
-                                w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, d_out, out_dtype, M, topk, H, I,
-                                E, flags, static_cast<char*>(workspace) + stage, workspace_bytes - stage, stream);
+                                w13_scale, w13_g, G13, w2_comp, w2_meta, w2_scale, w2_g, G2, out_target, out_dtype, M, topk, H,
+                                I, E, flags & ~B200FP4_MOE_HOST_DIRECT_OUT, static_cast<char*>(workspace) + stage,
+                                workspace_bytes - stage, stream, sc);
   if (rc != B200FP4_STATUS_SUCCESS) return rc;
-  int moe_status = 0;   // the layer's status word (hdr[3] of its plan) comes back with the result
-  if (cudaMemcpyAsync(out_host, d_out, nh, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
-      cudaMemcpyAsync(&moe_status, reinterpret_cast<const int*>(static_cast<char*>(workspace) + stage) + 3, sizeof(int),
-                      cudaMemcpyDeviceToHost, st) != cudaSuccess ||
-      cudaStreamSynchronize(st) != cudaSuccess) {
+  if (ev) {
+    if (cudaEventRecord(ev->consumed, st) != cudaSuccess) {
+      cudaGetLastError();
+      return B200FP4_STATUS_EXECUTION_FAILED;
+    }
+    ev->used = true;
+  }
+  // the layer's status word (hdr[3] of its plan) comes back with the result
+  if ((out_target == d_out && cudaMemcpyAsync(out_host, d_out, nh, cudaMemcpyDeviceToHost, st) != cudaSuccess) ||
+      (status_host && !sc.status_out && cudaMemcpyAsync(status_host, reinterpret_cast<const int*>(static_cast<char*>(workspace) + stage) + 3,
+                                      sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess)) {
+    cudaGetLastError();
+    return B200FP4_STATUS_EXECUTION_FAILED;
+  }
+  return B200FP4_STATUS_SUCCESS;
+}
+
+extern "C" int b200fp4_fused_sparse_moe_host(const void* hidden_host, int h_dtype, const float* topk_weights_host,
+                                             const int32_t* topk_ids_host, const int32_t* expert_map, int64_t global_E,
+                                             const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale,
+                                             const float* w13_g, int64_t G13, const uint8_t* w2_comp,
+                                             const uint8_t* w2_meta, const uint8_t* w2_scale, const float* w2_g,
+                                             int64_t G2, void* out_host, int out_dtype, int64_t M, int64_t topk,
+                                             int64_t H, int64_t I, int64_t E, int flags, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+  if (M == 0 && topk > 0 && H > 0 && I > 0 && E > 0) return B200FP4_STATUS_SUCCESS;
+  int moe_status = 0;
+  const int rc = b200fp4_fused_sparse_moe_host_async(hidden_host, h_dtype, topk_weights_host, topk_ids_host, expert_map,
+                                                     global_E, w13_comp, w13_meta, w13_scale, w13_g, G13, w2_comp, w2_meta,
+                                                     w2_scale, w2_g, G2, out_host, out_dtype, &moe_status, M, topk, H, I, E,
+                                                     flags, workspace, workspace_bytes, stream, nullptr);
+  if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) {
     cudaGetLastError();
     return B200FP4_STATUS_EXECUTION_FAILED;
   }

@@ -1,16 +1,22 @@
 """Expert-parallel MoE layers: E/G experts per GPU.
 
-Decode (`ExpertParallelMoE`): every rank packs its tokens into dispatch records (activation row, top-k
-global expert ids, router weights), one all-gather brings all ranks' records to every rank, the fused
-sparse MoE op runs over them with `expert_map` masking the experts the rank does not own (-1 entries
-are skipped by the plan kernel, so foreign pairs cost no weight traffic) and writes fp32 partial rows,
-and one reduce-scatter sums the partial rows of a token over the ranks and leaves each rank its own
-tokens.  With top-10 of 512 experts a token has an expert on nearly every rank, so "send a token only
-where it is needed" saves nothing over the all-gather, which is a single NCCL kernel over NVLink /
-NVSwitch instead of G-1 sends and receives per rank; the sizes are fixed, so no split-size exchange or
-host round trip sits on the decode path.  `mode="a2a"` keeps the earlier spelling (fixed-capacity
-all-to-all dispatch of G copies, all-to-all of 16-bit partial rows, fp32 sum at the source) for
-comparison.
+Decode (`ExpertParallelMoE`), three exchanges behind one interface:
+  mode="p2p" (default for CUDA ranks)  this library's own kernels over peer memory (torch symmetric memory gives
+      every rank the peers' buffer addresses): a dispatch kernel stores each token's record (activation row, top-k
+      global expert ids, router weights) into every rank's record buffer with plain NVLink stores and publishes a
+      step-numbered flag; the fused sparse MoE op runs over all ranks' records with `expert_map` masking the experts
+      the rank does not own (-1 entries are skipped by the plan kernel, so foreign pairs cost no weight traffic) and
+      its last kernel stores the fp32 partial rows straight into the owners' buffers; a combine kernel waits for the
+      peers' flags, sums the G partial rows of every token and rounds once.  No collective call per step; every wait
+      is bounded and reports through a status word (`p2p_status()`).
+  mode="gather"  the same with collectives of the process group: one all-gather of the records, the fused op,
+      one reduce-scatter of the fp32 partial rows (default for CPU stand-in ranks; what the benchmark falls back to
+      if the peer-memory exchange reports an expired wait).
+  mode="a2a"  fixed-capacity all-to-all dispatch of G copies, all-to-all of 16-bit partial rows, fp32 sum at the
+      source (kept for comparison).
+With top-10 of 512 experts a token has an expert on nearly every rank, so "send a token only where it is needed"
+saves nothing over sending every record everywhere; the sizes are fixed, so no split-size exchange or host round
+trip sits on the decode path.
 Prefill (`ExpertParallelMoEPrefill`): all-gather of the token block, grouped NVFP4 path over the local
 experts, reduce-scatter of the partial output rows.
 
@@ -89,6 +95,8 @@ class ExpertParallelMoE:
         self._bufs = {}
         self._flags = None
         self._bound = None
+        self._host_in = {}
+        self._copy_stream = None
         self._p2p = None
         self._seq = 0
 
@@ -291,21 +299,68 @@ class ExpertParallelMoE:
         return self._forward_cuda(hidden, topk_w, topk_ids, emap)
 
 
+    def _bound_layer(self, device):
+        if self._bound is None:
+            from . import sparse_fp4_v7 as sp7
+            k = ("comp_T", "meta_T", "scale_T", "g_scales")
+            self._bound = sp7.FusedSparseMoE(*[self.w13[x] for x in k], *[self.w2[x] for x in k], self.inter,
+                                             expert_map=self.expert_map(device))
+        return self._bound
+
     def forward_host(self, hidden_host, topk_w_host, topk_ids_host, out_host, device) -> torch.Tensor:
         """forward for CPU tensors (pinned for asynchronous copies); out_host is valid on return.  On one GPU this
         is a single call of the library's host-buffer entry point; with several ranks the copies bracket forward."""
         if self.world == 1 and self._fn is None:
-            if self._bound is None:
-                from . import sparse_fp4_v7 as sp7
-                k = ("comp_T", "meta_T", "scale_T", "g_scales")
-                self._bound = sp7.FusedSparseMoE(*[self.w13[x] for x in k], *[self.w2[x] for x in k], self.inter,
-                                                 expert_map=self.expert_map(device))
-            return self._bound.forward_host(hidden_host, topk_w_host, topk_ids_host, out_host=out_host)
-        out = self.forward(hidden_host.to(device, non_blocking=True), topk_w_host.to(device, non_blocking=True),
-                           topk_ids_host.to(device, non_blocking=True))
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream(device).synchronize()
+            return self._bound_layer(device).forward_host(hidden_host, topk_w_host, topk_ids_host, out_host=out_host)
+        self.submit_host(hidden_host, topk_w_host, topk_ids_host, out_host, device)
+        self.wait_host(device)
         return out_host
+
+    def submit_host(self, hidden_host, topk_w_host, topk_ids_host, out_host, device, slot: int = 0):
+        """forward_host without the wait, for a caller that keeps several steps in flight (every step in flight has
+        its own out_host).  Returns a CUDA event that completes when out_host holds the result; wait_host() waits for
+        everything submitted.  On one GPU the inputs of a step travel on a copy stream while the step before it
+        computes (steps alternate between staging buffers by `slot`)."""
+        if self.world == 1 and self._fn is None:
+            return self._bound_layer(device).submit_host(hidden_host, topk_w_host, topk_ids_host, out_host, slot=slot)
+        if self._fn is not None:        # CPU ranks (tests): nothing to queue
+            out_host.copy_(self.forward(hidden_host.to(device), topk_w_host.to(device), topk_ids_host.to(device)))
+            return None
+        # several ranks: the inputs travel on a copy stream into one of the staging slots while the previous step
+        # computes; the exchange, the local layer and the copy out follow on the current stream
+        cur = torch.cuda.current_stream(device)
+        key = (int(slot), tuple(hidden_host.shape), tuple(topk_ids_host.shape), hidden_host.dtype)
+        st = self._host_in.get(key)
+        if st is None:
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream(device=device)
+            st = self._host_in[key] = {
+                "h": torch.empty(hidden_host.shape, dtype=hidden_host.dtype, device=device),
+                "w": torch.empty(topk_w_host.shape, dtype=topk_w_host.dtype, device=device),
+                "ids": torch.empty(topk_ids_host.shape, dtype=topk_ids_host.dtype, device=device),
+                "loaded": torch.cuda.Event(), "consumed": torch.cuda.Event(), "used": False}
+        cs = self._copy_stream
+        with torch.cuda.stream(cs):
+            if st["used"]:
+                cs.wait_event(st["consumed"])
+            st["ids"].copy_(topk_ids_host, non_blocking=True)
+            st["w"].copy_(topk_w_host, non_blocking=True)
+            st["h"].copy_(hidden_host, non_blocking=True)
+            st["loaded"].record(cs)
+        cur.wait_event(st["loaded"])
+        out = self.forward(st["h"], st["w"], st["ids"])
+        st["consumed"].record(cur)
+        st["used"] = True
+        out_host.copy_(out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(cur)
+        return done
+
+    def wait_host(self, device) -> None:
+        if self.world == 1 and self._fn is None:
+            self._bound_layer(device).wait_host()
+            return
+        torch.cuda.current_stream(device).synchronize()
 
 
 class ExpertParallelMoEPrefill:

@@ -23,6 +23,8 @@ import torch
 from . import _lib
 from ._torch_util import dtype_code, ptr, require, require_cuda, stream_ptr, workspace
 
+STATUS_INTERNAL_ERROR = 14       # B200FP4_STATUS_INTERNAL_ERROR: a bounded device wait expired
+
 
 def _check_act(A: torch.Tensor, name: str) -> None:
     require(A.dim() == 2, f"{name} must be 2-D")
@@ -268,6 +270,8 @@ class FusedSparseMoE:
         self._lib = _lib.lib()
         self._fn = self._lib.b200fp4_fused_sparse_moe
         self._ws_bytes = {}
+        self._host_slots = {}
+        self._copy_stream = None
 
     def __call__(self, hidden_states, topk_weights, topk_ids, apply_router_weight_on_input: bool = False, out=None):
         M, H = hidden_states.shape
@@ -331,6 +335,60 @@ class FusedSparseMoE:
                 ws.data_ptr(), ws.numel(), stream_ptr(dev))
         _lib.check(rc, "fused_sparse_moe_v7 (host buffers)")
         return out_host
+
+
+    def submit_host(self, hidden_host, topk_weights_host, topk_ids_host, out_host, slot: int = 0,
+                    overlap_copies: bool = True, direct_out: bool = True, apply_router_weight_on_input: bool = False):
+        """forward_host without the wait: queues the copies in, the layer and the copy out and returns a CUDA event
+        that completes when out_host holds the result.  Steps submitted with different `slot` values use different
+        staging buffers, so with overlap_copies the inputs of one step travel (on a copy stream of this object) while
+        the previous step computes; every step in flight needs its own out_host.  With direct_out the layer's last
+        kernel stores the result rows and the status word straight into pinned host memory (no copy out is queued:
+        a copy between two layers costs the stream about 5 us).  wait_host() waits
+        for everything submitted and raises if a layer reported an expired wait."""
+        M, H = hidden_host.shape
+        topk = topk_ids_host.shape[1]
+        require(not hidden_host.is_cuda and not topk_weights_host.is_cuda and not topk_ids_host.is_cuda and
+                not out_host.is_cuda, "submit_host takes CPU tensors")
+        require(H == self.H and hidden_host.is_contiguous() and hidden_host.dtype in (torch.float16, torch.bfloat16),
+                "hidden_host must be a contiguous [M,H] 16-bit tensor")
+        require(topk_weights_host.dtype == torch.float32 and topk_ids_host.dtype == torch.int32 and
+                topk_weights_host.is_contiguous() and topk_ids_host.is_contiguous() and
+                tuple(topk_weights_host.shape) == (M, topk), "topk_weights f32 / topk_ids i32 must be contiguous [M, topk]")
+        require(out_host.is_contiguous() and tuple(out_host.shape) == (M, H) and
+                out_host.dtype in (torch.float16, torch.bfloat16), "out_host must be a contiguous [M,H] 16-bit CPU tensor")
+        require(hidden_host.is_pinned() and topk_weights_host.is_pinned() and topk_ids_host.is_pinned() and
+                out_host.is_pinned(), "submit_host needs pinned host tensors (pageable copies would block the queue)")
+        dev = self.device
+        key = ("host_slot", M, topk, int(slot))
+        st = self._host_slots.get(key)
+        if st is None:
+            nws = self._lib.b200fp4_fused_moe_host_workspace_bytes(M, topk, H, self.I, self.E)
+            st = self._host_slots[key] = (torch.empty(nws, dtype=torch.uint8, device=dev),
+                                          torch.zeros(1, dtype=torch.int32).pin_memory())
+        ws, status = st
+        if overlap_copies and self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=dev)
+        flags = self._flags | (_lib.MOE_ROUTER_WEIGHT_ON_INPUT if apply_router_weight_on_input else 0)
+        flags |= _lib.MOE_HOST_DIRECT_OUT if direct_out else 0
+        with torch.cuda.device(dev):
+            rc = self._lib.b200fp4_fused_sparse_moe_host_async(
+                hidden_host.data_ptr(), dtype_code(hidden_host.dtype), topk_weights_host.data_ptr(), topk_ids_host.data_ptr(),
+                *self._head, out_host.data_ptr(), dtype_code(out_host.dtype), status.data_ptr(), M, topk, H, self.I, self.E,
+                flags, ws.data_ptr(), ws.numel(), stream_ptr(dev),
+                self._copy_stream.cuda_stream if overlap_copies else None)
+            _lib.check(rc, "fused_sparse_moe_v7 (host buffers, queued)")
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(dev))
+        return done
+
+    def wait_host(self):
+        """Waits for every step queued by submit_host on the current stream and checks their status words."""
+        torch.cuda.current_stream(self.device).synchronize()
+        for _, status in self._host_slots.values():
+            if int(status[0]) != 0:
+                status.zero_()
+                raise _lib.B200Fp4Error(STATUS_INTERNAL_ERROR, "fused_sparse_moe_v7 (host buffers, queued)")
 
 
 def convert_weight_batch_to_v7(weights, scales, g_scales, device="cuda", batch_size=16):

@@ -174,6 +174,7 @@ B200FP4_API int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, con
 #define B200FP4_MOE_ROUTER_WEIGHT_ON_INPUT 1
 #define B200FP4_SPARSE_META_ORDERED 2
 #define B200FP4_MOE_SEPARATE_LAUNCHES 4   /* fused layer: one launch per projection even where one cooperative launch is possible */
+#define B200FP4_MOE_HOST_DIRECT_OUT 8     /* b200fp4_fused_sparse_moe_host_async only, see there */
 
 B200FP4_API size_t b200fp4_sparse_workspace_bytes(int64_t P, int64_t K, int64_t E);
 
@@ -286,6 +287,34 @@ B200FP4_API int b200fp4_fused_sparse_moe_host(
     int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
     const float* w2_g, int64_t G2, void* out_host, int out_dtype, int64_t M, int64_t topk, int64_t H,
     int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Enqueue-only form of b200fp4_fused_sparse_moe_host for a caller that keeps several steps in flight: the
+ * three copies in, the layer and the copies out are queued and the call returns without waiting.
+ *   copy_stream   NULL: everything runs on `stream`.  Otherwise the copies in run on copy_stream and
+ *                 the layer waits for them through an event, so the inputs of the next step travel
+ *                 while this step computes; before it overwrites the staging buffers of `workspace`
+ *                 copy_stream waits for the layer of the previous submission that used the same
+ *                 workspace -- a caller that alternates two workspaces gets the overlap, one that
+ *                 reuses a single workspace stays correct.  The events live in a table of 32
+ *                 (workspace, device) entries; ALLOC_FAILED beyond that.
+ *   status_host   NULL, or host memory (pinned) that receives the layer's status word after the result
+ *                 (0, or B200FP4_MOE_STATUS_WAIT_EXPIRED).
+ *   flags         those of b200fp4_fused_sparse_moe, and B200FP4_MOE_HOST_DIRECT_OUT: where out_host
+ *                 (and status_host) is pinned memory that the device can address, the layer's last
+ *                 kernel stores the result rows (and the status word) straight into it over the host
+ *                 link and no copy out is queued for it -- a copy between two layers costs the stream
+ *                 about 5 us of engine switching; for pageable memory the flag changes nothing.
+ * out_host and status_host are valid once the work queued on `stream` has completed (synchronise the
+ * stream or an event recorded after the call); the caller gives every step in flight its own out_host.
+ * No counterpart in the reference, which is always called with device tensors. */
+B200FP4_API int b200fp4_fused_sparse_moe_host_async(
+    const void* hidden_host, int h_dtype, const float* topk_weights_host,
+    const int32_t* topk_ids_host, const int32_t* expert_map, int64_t global_E,
+    const uint8_t* w13_comp, const uint8_t* w13_meta, const uint8_t* w13_scale, const float* w13_g,
+    int64_t G13, const uint8_t* w2_comp, const uint8_t* w2_meta, const uint8_t* w2_scale,
+    const float* w2_g, int64_t G2, void* out_host, int out_dtype, int32_t* status_host, int64_t M,
+    int64_t topk, int64_t H, int64_t I, int64_t E, int flags, void* workspace, size_t workspace_bytes,
+    void* stream, void* copy_stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Part 4 -- grouped (per-expert) NVFP4 GEMM for MoE prefill and its routing helpers.

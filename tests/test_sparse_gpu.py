@@ -334,6 +334,31 @@ def test_bound_layer_host_buffers_match_device_call():
         layer.forward_host(hidden, tw, ids.long())
 
 
+@pytest.mark.parametrize("overlap,direct", [(True, True), (True, False), (False, True), (False, False)])
+def test_bound_layer_queued_host_steps_match_device_call(overlap, direct):
+    """submit_host keeps several steps in flight (copy stream + two staging slots, or everything on one stream);
+    every step's host result equals the device call on that step's inputs, also when a slot is reused at once."""
+    from dgx_vllm_b200 import sparse_fp4_v7 as sp7
+    E, H, I, B, topk = 16, 1024, 256, 9, 4
+    w13, w2, _, _, _ = _moe_case(E, H, I, B, topk, seed=81)
+    c = lambda d: [d[k].cuda() for k in ("comp_T", "meta_T", "scale_T", "g_scales")]
+    layer = sp7.FusedSparseMoE(*c(w13), *c(w2), I)
+    steps = []
+    for i in range(6):
+        _, _, tw, ids, hidden = _moe_case(E, H, I, B, topk, seed=200 + i)
+        steps.append((hidden.pin_memory(), tw.pin_memory(), ids.pin_memory(), torch.empty_like(hidden).pin_memory()))
+    refs = [layer(h.cuda(), w.cuda(), i.cuda()).cpu() for h, w, i, _ in steps]
+    slots = (0, 1, 0, 0, 1, 1)          # alternating and back-to-back reuse of a staging slot
+    events = [layer.submit_host(h, w, i, o, slot=slots[n], overlap_copies=overlap, direct_out=direct) for n, (h, w, i, o) in enumerate(steps)]
+    events[2].synchronize()
+    assert torch.equal(steps[2][3], refs[2])
+    layer.wait_host()
+    for (_, _, _, o), ref in zip(steps, refs):
+        assert torch.equal(o, ref)
+    with pytest.raises(RuntimeError):
+        layer.submit_host(steps[0][0].clone(), steps[0][1], steps[0][2], steps[0][3])     # pageable input
+
+
 @pytest.mark.parametrize("M,topk,E,H,I,separate", [
     (64, 8, 16, 2048, 512, False),      # 32 tokens per expert on average: eight-token passes, one launch
     (64, 8, 16, 2048, 512, True),       # ... and one launch per projection
