@@ -136,7 +136,8 @@ B200FP4_API int b200fp4_experts_quantize_scatter(const void* x, int in_dtype, in
  *             (b200fp4_sf_swizzled_bytes(rows, K/16) bytes each)
  *   alpha     device pointer to one f32 (= 1 / (global_scale_a * global_scale_b))
  *   out       [M, N] bf16, f16 or f32 (f32: the accumulator times alpha, unrounded)
- *   tile_n    0 = choose; 128 or 256 forces the CTA tile width (128 x tile_n output tiles)
+ *   tile_n    0 = choose; 128 or 256 forces the CTA tile width (128 x tile_n output tiles);
+ *             512 forces 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2; 16-bit output only)
  *   workspace b200fp4_gemm_workspace_bytes() bytes; its first int is a status word the kernel
  *             leaves at 0 unless one of its bounded barrier waits expired (then nothing it wrote
  *             may be trusted): read it after synchronising when diagnosing.

@@ -71,6 +71,24 @@ def test_shapes(M, N, K, tile_n):
     assert rel_err(out, ref) < TOL
 
 
+@pytest.mark.parametrize("M,N,K", [
+    (256, 256, 256),                 # one pair tile, one stage
+    (128, 256, 256), (1, 128, 64),   # the second CTA's rows lie entirely past M
+    (7, 384, 320), (200, 384, 320),  # M, N and K tails
+    (512, 768, 1024),                # several pair tiles and stages (the rings wrap)
+    (300, 1024, 4096),               # more stages than ring slots, several tiles per pair
+    (2304, 2560, 1024),              # more pair tiles than pairs of SMs: every pair takes a second tile
+])
+def test_pair_kernel_shapes(M, N, K):
+    """tile_n=512 selects the CTA-pair kernel (tcgen05 cta_group::2, 256x256 tiles)."""
+    out, ref, status = _run(*_rand(M, N, K, M + N + K + 1), tile_n=512)
+    assert status == 0
+    assert out.shape == (M, N)
+    assert rel_err(out, ref) < TOL
+    out16, ref16, status16 = _run(*_rand(M, N, K, M + N + K + 2), out_dtype=torch.float16, tile_n=512)
+    assert status16 == 0 and rel_err(out16, ref16) < TOL
+
+
 def test_fp16_output_and_in_place_and_determinism():
     from dgx_vllm_b200 import cutlass_scaled_fp4_mm
     x, w = _rand(64, 256, 512, 3)
