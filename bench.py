@@ -208,7 +208,26 @@ class L2Flush:
         self.sink = self.rd.sum()
 
 
-def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
+def _vllm_fp4_mm_us(timed, xc, wc, xs, ws, alpha, out, steps):
+    """Time vLLM's cutlass_scaled_fp4_mm on the same operands (same cold-L2 protocol); a string says why not."""
+    import torch
+    try:
+        from vllm import _custom_ops as vops
+        f8 = torch.float8_e4m3fn
+        xs8, ws8 = xs.view(f8), ws.view(f8)
+        ref = vops.cutlass_scaled_fp4_mm(xc, wc, xs8, ws8, alpha, torch.bfloat16)
+        torch.cuda.synchronize()
+        if tuple(ref.shape) != tuple(out.shape):
+            return "unavailable: unexpected result shape"
+        diff = float((ref.float() - out.float()).abs().max() / out.float().abs().max().clamp_min(1e-30))
+        if not diff < 2e-2:
+            return f"unavailable: result differs from this library's by {diff:.3g}"
+        return timed(lambda: vops.cutlass_scaled_fp4_mm(xc, wc, xs8, ws8, alpha, torch.bfloat16), steps) * 1e6
+    except Exception as e:          # not built for this GPU, symbol missing, import failure
+        return f"unavailable: {type(e).__name__}: {str(e)[:120]}"
+
+
+def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10, library: bool = True):
     """Secondary measurements reported next to the headline: dense NVFP4 GEMM (BASELINE configs[1]:
     N=14336, K=4096, M in {128,1024,4096}, activation quantized on the fly) and the quantizer alone.
     Each iteration is timed on its own with CUDA events after rewriting a 256 MiB buffer (cold L2)."""
@@ -257,6 +276,31 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10):
             "frac_of_nominal_fp4_peak": flops / t_mm / 1e12 / fp4_nominal,
             "hbm_GBps": byt / t_mm / 1e9, "frac_of_measured_hbm": byt / t_mm / 1e9 / hbm_peak,
             "bound": "hbm" if M < 316 else "tensor"}
+        # the serving stack's own library kernel for the same op on the same tensors, when this image's vLLM build has it
+        # (comparison only: nothing in this package calls it)
+        if library:
+            parts[f"dense_gemm_m{M}"]["vllm_cutlass_scaled_fp4_mm_us"] = _vllm_fp4_mm_us(timed, xc, wc, xs, ws, alpha, out, steps)
+        if M == 4096:
+            # the same GEMM back to back for about half a second, with the clocks sampled: what the part sustains
+            # under its power limit, and at which SM clock
+            n_loop = 4000
+            sampler = ClockSampler(dev.index or 0)
+            sampler.start()
+            for _ in range(20):
+                cutlass_scaled_fp4_mm(xc, wc, xs, ws, alpha, torch.bfloat16, out=out)
+            torch.cuda.synchronize()
+            time.sleep(0.05)
+            sampler.begin()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n_loop):
+                cutlass_scaled_fp4_mm(xc, wc, xs, ws, alpha, torch.bfloat16, out=out)
+            b.record()
+            torch.cuda.synchronize()
+            sampler.end()
+            t_loop = a.elapsed_time(b) * 1e-3 / n_loop
+            parts[f"dense_gemm_m{M}"]["back_to_back"] = {"gemm_us": t_loop * 1e6, "tflops": flops / t_loop / 1e12,
+                                                         "launches": n_loop, "clocks": sampler.stop()}
     for M in (4096, 16384):
         x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
         gx = synth.global_scale_of(x)
@@ -707,10 +751,21 @@ def main():
     ap.add_argument("--only-prefill", action="store_true",
                     help="run just the grouped prefill layer (the `moe_prefill_8192_tokens` part) and print its numbers; "
                          "a short command for profiling that path")
+    ap.add_argument("--only-dense", action="store_true",
+                    help="run just the dense GEMM / quantizer parts and print their numbers; a short command for "
+                         "profiling those kernels (with --no-library-comparison the serving stack's kernel is not timed)")
+    ap.add_argument("--no-library-comparison", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
+    if args.only_dense:
+        import torch
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        hbm_peak, _ = measured_peaks()
+        print(json.dumps(bench_dense_parts(dev, L2Flush(dev), hbm_peak, library=not args.no_library_comparison)))
+        return 0
     if args.only_prefill:
         import torch
         dev = torch.device("cuda", 0)
