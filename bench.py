@@ -234,6 +234,7 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10, library: bool = Tru
     import torch
     import synth
     from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant
+    from dgx_vllm_b200.ops import nvfp4_linear
 
     def timed(fn, n):
         ts = []
@@ -265,9 +266,8 @@ def bench_dense_parts(dev, flush, hbm_peak, steps: int = 10, library: bool = Tru
         xc, xs = scaled_fp4_quant(x, gx)
         t_mm = timed(lambda: cutlass_scaled_fp4_mm(xc, wc, xs, ws, alpha, torch.bfloat16, out=out), steps)
 
-        def both():
-            c, s_ = scaled_fp4_quant(x, gx)
-            cutlass_scaled_fp4_mm(c, wc, s_, ws, alpha, torch.bfloat16, out=out)
+        def both():      # what a quantized linear layer does per forward: one library call for quantizer + GEMM
+            nvfp4_linear(x, gx, wc, ws, alpha, out=out)
         t_all = timed(both, steps)
         flops = 2.0 * M * N * K
         byt = N * K * 0.5625 + M * K * 0.5625 + 2.0 * M * N

@@ -80,6 +80,8 @@ SIGNATURES = {
     "b200fp4_fused_moe_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
     "b200fp4_fused_sparse_moe_host": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp,
                                              _i64, _vp, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
+    "b200fp4_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "b200fp4_linear_nvfp4": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "b200fp4_fused_sparse_moe_host_async": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp,
                                                    _vp, _i64, _vp, _i32, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _sz,
                                                    _vp, _vp]),

@@ -988,6 +988,35 @@ extern "C" int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, cons
   return finish_launch(1);
 }
 
+// ---------------------------------------------------------------------------------------- linear layer in one call
+
+// y = NVFP4(x) @ W^T: the activation quantizer and the GEMM queued by one call (two launches a few microseconds apart;
+// through two Python calls the GPU idles between them for longer than either kernel runs at prefill sizes).
+// workspace: [codes M*K/2 | swizzled block scales | GEMM workspace], each part 256-byte aligned.
+static size_t linear_part(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t b200fp4_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M < 0 || N <= 0 || K <= 0 || (K % 16) != 0) return 0;
+  return linear_part((size_t)M * (size_t)K / 2) + linear_part(b200fp4_sf_swizzled_bytes(M, K / 16)) +
+         linear_part(b200fp4_gemm_workspace_bytes(M, N, K));
+}
+
+extern "C" int b200fp4_linear_nvfp4(const void* x, int x_dtype, int64_t ldx, const float* x_global_scale, const void* w_codes,
+                                    const void* w_sf, const float* alpha, void* out, int out_dtype, int64_t M, int64_t N,
+                                    int64_t K, int tile_n, void* workspace, size_t workspace_bytes, void* stream) {
+  if (M < 0 || N <= 0 || K <= 0 || (K % 64) != 0) return B200FP4_STATUS_INVALID_VALUE;
+  if (M == 0) return B200FP4_STATUS_SUCCESS;
+  if (!workspace || !aligned(workspace, 256) || workspace_bytes < b200fp4_linear_workspace_bytes(M, N, K))
+    return B200FP4_STATUS_ALLOC_FAILED;
+  unsigned char* codes = static_cast<unsigned char*>(workspace);
+  unsigned char* sf = codes + linear_part((size_t)M * (size_t)K / 2);
+  unsigned char* gemm_ws = sf + linear_part(b200fp4_sf_swizzled_bytes(M, K / 16));
+  int rc = b200fp4_quantize(x, x_dtype, M, K, ldx, x_global_scale, codes, sf, 1, stream);
+  if (rc != B200FP4_STATUS_SUCCESS) return rc;
+  return b200fp4_gemm_nvfp4(codes, w_codes, sf, w_sf, alpha, out, out_dtype, M, N, K, tile_n, gemm_ws,
+                            b200fp4_gemm_workspace_bytes(M, N, K), stream);
+}
+
 // ---------------------------------------------------------------------------------------- grouped entry points
 
 extern "C" size_t b200fp4_grouped_gemm_workspace_bytes(int64_t rows_capacity, int64_t E) {

@@ -57,14 +57,13 @@ class ColumnShardedNvfp4Linear:
         if self._fn is not None:
             y = self._fn(x, self)
         else:
-            from .ops import cutlass_scaled_fp4_mm, scaled_fp4_quant
-            xc, xs = scaled_fp4_quant(x, x_global_scale)
+            from .ops import nvfp4_linear
             a = self._alpha
             if a is None or a[0] is not x_global_scale or a[1] != x_global_scale._version:
                 a = (x_global_scale, x_global_scale._version, (1.0 / (x_global_scale * self.gw)).to(torch.float32))
                 self._alpha = a
             alpha = a[2]
-            y = cutlass_scaled_fp4_mm(xc, self.codes, xs, self.sf, alpha, x.dtype)
+            y = nvfp4_linear(x, x_global_scale, self.codes, self.sf, alpha)      # quantizer + GEMM in one library call
         if not gather or self.world == 1:
             return y
         parts = [torch.empty_like(y) for _ in range(self.world)]

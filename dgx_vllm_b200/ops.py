@@ -72,6 +72,48 @@ def cutlass_scaled_fp4_mm(a: torch.Tensor, b: torch.Tensor, block_scale_a: torch
     return out
 
 
+_linear_ws = {}
+
+
+def nvfp4_linear(x: torch.Tensor, x_global_scale: torch.Tensor, w_codes: torch.Tensor, w_block_scale: torch.Tensor,
+                 alpha: torch.Tensor, *, out: torch.Tensor | None = None, tile_n: int = 0) -> torch.Tensor:
+    """y[M,N] = alpha * NVFP4(x) @ W^T: scaled_fp4_quant followed by cutlass_scaled_fp4_mm in ONE library call
+    (b200fp4_linear_nvfp4), which is what a quantized linear layer does on every forward (the pair of ops in vLLM's
+    NVFP4 linear apply, nvfp4_utils.py; emulated by the reference at fix_nvfp4_emulation_backend.py:60-102).  Same bytes
+    as calling the two ops; the launches are a few microseconds apart instead of a Python call apart.
+    x [M,K] bf16/f16 (rows may be strided), w_codes [N,K/2] u8, w_block_scale swizzled, alpha / x_global_scale one f32."""
+    dev = require_cuda(x, x_global_scale, w_codes, w_block_scale, alpha)
+    require(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16) and x.stride(1) == 1, "x must be [M,K] bf16/f16, unit inner stride")
+    require(w_codes.dim() == 2 and w_codes.dtype == torch.uint8 and w_codes.is_contiguous() and w_codes.shape[1] * 2 == x.shape[1],
+            "w_codes must be contiguous [N,K/2] uint8")
+    M, K = x.shape
+    N = w_codes.shape[0]
+    require(K % 64 == 0, "K must be a multiple of 64")
+    L = _lib.lib()
+    require(w_block_scale.is_contiguous() and
+            w_block_scale.element_size() * w_block_scale.numel() >= L.b200fp4_sf_swizzled_bytes(N, K // 16),
+            "w_block_scale must be the swizzled scale tensor of the weight")
+    require(alpha.dtype == torch.float32 and alpha.numel() == 1 and x_global_scale.dtype == torch.float32 and
+            x_global_scale.numel() == 1, "alpha and x_global_scale must be one f32 each")
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=dev)
+    else:
+        require(out.is_cuda and out.dtype in (torch.bfloat16, torch.float16) and tuple(out.shape) == (M, N) and
+                out.is_contiguous(), "out must be a contiguous [M,N] 16-bit CUDA tensor")
+    if M == 0:
+        return out
+    need = L.b200fp4_linear_workspace_bytes(M, N, K)
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _linear_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _linear_ws[key] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.b200fp4_linear_nvfp4(ptr(x), dtype_code(x.dtype), x.stride(0) if M > 1 else K, ptr(x_global_scale),
+                                          ptr(w_codes), ptr(w_block_scale), ptr(alpha), ptr(out), dtype_code(out.dtype), M, N, K,
+                                          tile_n, ptr(ws), ws.numel(), stream_ptr(dev)), "nvfp4_linear")
+    return out
+
+
 def last_gemm_status(device=None) -> int:
     """Status word of the most recent GEMM on the current stream of `device` (0 = ok).  Synchronises."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -150,11 +150,15 @@ class Nvfp4LinearCore:
 
     def apply_weights(self, layer, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         from . import ops
-        quant, mm = self._quant or ops.scaled_fp4_quant, self._mm or ops.cutlass_scaled_fp4_mm
         out_shape = [*x.shape[:-1], layer.output_size_per_partition]
         x2 = x.reshape(-1, x.shape[-1])
-        codes, sf = quant(x2, layer.input_global_scale_inv, True)
-        out = mm(codes, layer.weight, sf, layer.weight_scale, layer.alpha, x.dtype)
+        if self._quant is None and self._mm is None:
+            # quantizer and GEMM queued by one library call
+            out = ops.nvfp4_linear(x2, layer.input_global_scale_inv, layer.weight, layer.weight_scale, layer.alpha)
+        else:
+            quant, mm = self._quant or ops.scaled_fp4_quant, self._mm or ops.cutlass_scaled_fp4_mm
+            codes, sf = quant(x2, layer.input_global_scale_inv, True)
+            out = mm(codes, layer.weight, sf, layer.weight_scale, layer.alpha, x.dtype)
         if bias is not None:
             out = out + bias
         return out.view(*out_shape)

@@ -148,6 +148,18 @@ B200FP4_API int b200fp4_gemm_nvfp4(const void* a_codes, const void* b_codes, con
                                    int64_t M, int64_t N, int64_t K, int tile_n, void* workspace,
                                    size_t workspace_bytes, void* stream);
 
+/* The whole linear layer y = NVFP4(x) @ W^T in one call: b200fp4_quantize (swizzled scales) into the workspace, then
+ * b200fp4_gemm_nvfp4.  What NvFp4LinearKernel.apply_weights does with two ops (scaled_fp4_quant then
+ * cutlass_scaled_fp4_mm: vllm/model_executor/layers/quantization/utils/nvfp4_utils.py, the call pair the reference's
+ * emulation replaces at fix_nvfp4_emulation_backend.py:60-102); one host call keeps the two launches a few
+ * microseconds apart.  x [M, K] bf16/f16 with row stride ldx; x_global_scale, alpha device pointers as above.
+ * workspace: b200fp4_linear_workspace_bytes(M, N, K) bytes, 256-byte aligned. */
+B200FP4_API size_t b200fp4_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+B200FP4_API int b200fp4_linear_nvfp4(const void* x, int x_dtype, int64_t ldx, const float* x_global_scale,
+                                     const void* w_codes, const void* w_sf, const float* alpha, void* out,
+                                     int out_dtype, int64_t M, int64_t N, int64_t K, int tile_n,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Part 3 -- 2:4-sparse / dense NVFP4 batched GEMV for MoE decode.
  * Replace the pybind functions of sparse_fp4_kernel/sparse_fp4_v7.cu:744-749.

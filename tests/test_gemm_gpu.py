@@ -109,6 +109,29 @@ def test_fp16_output_and_in_place_and_determinism():
         cutlass_scaled_fp4_mm(xc, wc, xs[:64], ws, alpha, torch.bfloat16)                 # scale tensor too small
 
 
+def test_linear_in_one_call_matches_the_two_ops():
+    """nvfp4_linear (quantizer + GEMM queued by one library call) returns the bytes of scaled_fp4_quant followed by
+    cutlass_scaled_fp4_mm, for contiguous and row-strided activations, small and pair-kernel sizes."""
+    from dgx_vllm_b200 import cutlass_scaled_fp4_mm, scaled_fp4_quant
+    from dgx_vllm_b200.ops import last_gemm_status, nvfp4_linear
+    for M, N, K in ((9, 384, 320), (300, 512, 1024), (2304, 2560, 1024)):
+        x, w = _rand(M, N, K, 5 + M)
+        gx, gw = float(oracle.global_scale(x.float().numpy())), float(oracle.global_scale(w.float().numpy()))
+        wc, ws = _quant_gpu(w, gw)
+        gxt = torch.tensor([gx], dtype=torch.float32, device="cuda")
+        alpha = torch.tensor([1.0 / (np.float32(gx) * np.float32(gw))], dtype=torch.float32, device="cuda")
+        xd = x.cuda()
+        xc, xs = scaled_fp4_quant(xd, gxt)
+        ref = cutlass_scaled_fp4_mm(xc, wc, xs, ws, alpha, torch.bfloat16)
+        assert last_gemm_status() == 0
+        assert torch.equal(nvfp4_linear(xd, gxt, wc, ws, alpha), ref)
+        wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device="cuda")
+        wide[:, :K] = xd
+        assert torch.equal(nvfp4_linear(wide[:, :K], gxt, wc, ws, alpha), ref)
+    with pytest.raises(RuntimeError):
+        nvfp4_linear(xd.float(), gxt, wc, ws, alpha)
+
+
 def test_prefill_config_m128_full_weight():
     # dense prefill configuration at M=128: N=14336, K=4096, checked in full
     out, ref, status = _run(*_rand(128, 14336, 4096, 11))
