@@ -1042,11 +1042,15 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
 // Epilogue from registers: the lane that holds 16 consecutive columns of a token writes them with 16-byte stores;
 // with SiLU the warp's 128 columns are 64 gate + the matching 64 up columns, the two halves of the warp swap one
 // token's values through shuffles, and SiLU(gate)*up leaves in fragment order for the down projection.
+// Two shapes of the same ring budget: 16 warps x 4 stages per block (the default), or 8 warps x 8 stages for launches with
+// few items (expert parallelism: a rank that owns 64 experts has about 550 gate_up items for 2368 warps; what bounds such
+// a launch is how many bytes ONE warp keeps in flight, so the idle warps' ring space goes to the busy ones).
 constexpr int kWsStages = 4;
 constexpr int kWsWarps = 16;
 constexpr int kWsThreads = 32 * kWsWarps;
 constexpr int kWsStageBytes = 14 * 128 + 512;     // 8 compressed + 4 metadata + 2 scale rows of 128 bytes, B fragments of 8 tokens
 constexpr size_t kWsSmemBytes = (size_t)kWsWarps * kWsStages * kWsStageBytes + 128;
+// (warps per block = 64 / stages, so both shapes use the same shared memory)
 
 // Lane-constant shared-memory offsets of the warp-scheduled kernel.
 // Stage layout: compressed rows 0..7 | metadata rows 0..3 | scale rows 0..1 (128 bytes each) | B fragments.  The 16-byte
@@ -1059,6 +1063,7 @@ struct WsLane {
   int lane, q, t, fr, fc;
 };
 
+template <int kS = kWsStages>
 __device__ __forceinline__ WsLane ws_lane(unsigned char* smem) {
   WsLane L;
   L.lane = threadIdx.x & 31;
@@ -1067,7 +1072,7 @@ __device__ __forceinline__ WsLane ws_lane(unsigned char* smem) {
   L.t = L.lane & 3;
   L.fr = L.lane >> 3;
   L.fc = L.lane & 7;
-  L.ring = ((shared_addr(smem) + 127u) & ~127u) + (uint32_t)warp * (kWsStages * kWsStageBytes);
+  L.ring = ((shared_addr(smem) + 127u) & ~127u) + (uint32_t)warp * (kS * kWsStageBytes);
   L.d_comp = (uint32_t)L.fr * 128u + (uint32_t)((L.fc ^ (2 * (L.fr & 3))) << 4);
   L.d_meta = 1024u + (uint32_t)L.fr * 128u + (uint32_t)((L.fc ^ (4 * (L.fr >> 1))) << 4);
   L.d_scale = 1536u + (uint32_t)L.fr * 128u + (uint32_t)L.fc * 16u;
@@ -1086,12 +1091,12 @@ __device__ __forceinline__ WsLane ws_lane(unsigned char* smem) {
 // for that pass -- are fetched only once done[pass] has reached `need`), 0 = stand-alone.
 // A consumer only ever waits for items that running warps hold (an item of the first projection is claimed before any
 // item of the second), so the wait cannot deadlock; it is bounded all the same and reports through the status word.
-template <bool kSilu, int kN, int kDep>
+template <bool kSilu, int kN, int kDep, int kS = kWsStages>
 __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const int base, int first, const WsLane& L,
                                         int* done, const int need) {
   const int lane = L.lane, q = L.q, t = L.t;
   const int N = kN ? kN : g.N;
-  const int nblk = g.K >> 7;                 // blocks of four 32-wide k-steps
+  const int nblk = g.K / (32 * kS);          // blocks of kS 32-wide k-steps (one turn of the ring)
   const int groups = g.n_slabs;              // 128-column groups per pass
   const int n_items = g.plan.hdr[1] * groups;
   if (first - base >= n_items) return first;
@@ -1186,17 +1191,17 @@ __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const i
     }
     cp_async_commit();
   };
-  auto advance = [&](Fetch& f) {     // four k-steps on
-    f.pc += (int64_t)32 * N;
-    f.pm += (int64_t)16 * N;
-    f.ps += (int64_t)8 * N;
-    f.pb += 128;
+  auto advance = [&](Fetch& f) {     // kS k-steps on
+    f.pc += (int64_t)(8 * kS) * N;
+    f.pm += (int64_t)(4 * kS) * N;
+    f.ps += (int64_t)(2 * kS) * N;
+    f.pb += 32 * kS;
   };
 
   Item cur = describe(first);
   Fetch F = sources(cur);
 #pragma unroll
-  for (int u = 0; u < 4; ++u) fetch(F, u);      // k-steps 0..3 of the first item
+  for (int u = 0; u < kS; ++u) fetch(F, u);     // the first kS k-steps of the first item
   advance(F);
   int carry;
 
@@ -1213,8 +1218,8 @@ __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const i
     for (int b = 0; b < nblk; ++b) {
       if (b == nblk - 1) F = sources(nxt);     // the last block of an item prefetches the first block of the next one
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        cp_async_wait<3>();
+      for (int u = 0; u < kS; ++u) {
+        cp_async_wait<kS - 1>();
         __syncwarp();
         const uint32_t st = L.ring + (uint32_t)u * kWsStageBytes;
         const uint4 v0 = lds128_at(st + L.off_comp), v1 = lds128_at(st + L.off_comp + 512u);
@@ -1222,7 +1227,7 @@ __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const i
         const uint4 s0 = lds128_at(st + L.off_scale), s1 = lds128_at(st + L.off_scale + 128u);
         const uint4 bv = lds128_at(st + L.d_b);
         const uint32_t bf[4] = {bv.x, bv.y, bv.z, bv.w};
-        fetch(F, u);                 // k-step four ahead, into the slot that was just read
+        fetch(F, u);                 // k-step kS ahead, into the slot that was just read
         uint32_t em[4];
         em[0] = prmt(m0.x, m1.x, 0x5140u);
         em[1] = prmt(m0.x, m1.x, 0x7362u);
@@ -1347,19 +1352,19 @@ __global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const Gem
 // Both projections of the MoE layer in one launch: the claim sequence runs through the gate_up items and on into the
 // down items, so a warp that finds no gate_up item left starts on the down projection of passes that are complete
 // instead of idling until the slowest warp of a first launch has finished and a second launch has ramped up.
-template <int kNA, int kNB>
-__global__ void __launch_bounds__(kWsThreads, 1)
+template <int kNA, int kNB, int kS = kWsStages>
+__global__ void __launch_bounds__(32 * (kWsStages * kWsWarps / kS), 1)
     fused_moe_ws_kernel(const GemvArgs ga, const GemvArgs gb, int* counter, int* done, int need) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch_dependents();
-  const WsLane L = ws_lane(smem);
+  const WsLane L = ws_lane<kS>(smem);
   int first = 0;
   if (L.lane == 0) first = atomicAdd(counter, 1);
   first = __shfl_sync(0xffffffffu, first, 0);
   const int n_a = ga.plan.hdr[1] * ga.n_slabs;
-  first = ws_phase<true, kNA, 1>(ga, counter, 0, first, L, done, need);
-  ws_phase<false, kNB, 2>(gb, counter, n_a, first, L, done, need);
+  first = ws_phase<true, kNA, 1, kS>(ga, counter, 0, first, L, done, need);
+  ws_phase<false, kNB, 2, kS>(gb, counter, n_a, first, L, done, need);
 }
 
 // ------------------------------------------------------------------------------------------ generic
@@ -1669,13 +1674,17 @@ int run_projection_ws(const SparseWeights& w, const Plan& plan, const __half* A,
   return N == 2048 ? launch_ws_t<false, 2048>(g, counter, items, st) : launch_ws_t<false, 0>(g, counter, items, st);
 }
 
-template <int kNA, int kNB>
+template <int kNA, int kNB, int kS = kWsStages>
 int launch_fused_ws_t(const GemvArgs& ga, const GemvArgs& gb, int* counter, int* done, int need, int64_t max_items,
                       cudaStream_t st) {
   static bool attr_set[64] = {false};
-  if (!ws_prepare(fused_moe_ws_kernel<kNA, kNB>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
-  launch_pdl(fused_moe_ws_kernel<kNA, kNB>, dim3((unsigned)ws_grid(max_items)), dim3(kWsThreads), kWsSmemBytes, st, ga, gb,
-             counter, done, need);
+  constexpr int warps = kWsStages * kWsWarps / kS;
+  if (!ws_prepare(fused_moe_ws_kernel<kNA, kNB, kS>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
+  int64_t grid = (max_items + warps - 1) / warps;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  if (grid < 1) grid = 1;
+  launch_pdl(fused_moe_ws_kernel<kNA, kNB, kS>, dim3((unsigned)grid), dim3(32 * warps), kWsSmemBytes, st, ga, gb, counter, done,
+             need);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -2084,8 +2093,20 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
       gb.n_slabs = (int)(H / 128);
       const int need = ga.n_slabs + g_wait_extra_need;
       const int64_t items = max_passes(P, E) * (ga.n_slabs + gb.n_slabs);
-      if (2 * I == 1024 && H == 2048) rc = launch_fused_ws_t<1024, 2048>(ga, gb, plan.hdr + 2, done, need, items, st);
-      else rc = launch_fused_ws_t<0, 0>(ga, gb, plan.hdr + 2, done, need, items, st);
+      // Few items (a rank of an expert-parallel group owns few experts): eight warps with eight-stage rings per block.
+      // The host only knows bounds: local pairs ~ P * E / global_E, passes of the first projection ~ min(E, local pairs).
+      const int64_t local_pairs = (expert_map && global_E > 0) ? P * E / global_E : P;
+      const int64_t est_items_a = (local_pairs < E ? local_pairs : E) * ga.n_slabs;
+      // (measured at 8 ranks x 32 tokens, 64 local experts: the GEMV launch takes 49.7 us with 16 warps x 4 stages,
+      // 37.6 us with 8 x 8, 44.7 us with 4 x 16)
+      const bool deep = est_items_a <= (int64_t)sm_count() * 8 && H % 256 == 0 && I % 256 == 0;
+      if (2 * I == 1024 && H == 2048) {
+        rc = deep ? launch_fused_ws_t<1024, 2048, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
+                  : launch_fused_ws_t<1024, 2048>(ga, gb, plan.hdr + 2, done, need, items, st);
+      } else {
+        rc = deep ? launch_fused_ws_t<0, 0, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
+                  : launch_fused_ws_t<0, 0>(ga, gb, plan.hdr + 2, done, need, items, st);
+      }
       if (rc != B200FP4_STATUS_SUCCESS) return rc;
       if (g_prof_events[1]) cudaEventRecord(g_prof_events[1], st);
     } else {
