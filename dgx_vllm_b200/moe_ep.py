@@ -386,6 +386,9 @@ class ExpertParallelMoEPrefill:
         self._fn = local_fn
         self._emap = None
         self._alphas = None
+        self._bufs = {}
+        self._graphs = {}
+        self.use_graph = local_fn is None      # CUDA ranks: the local layer's dozen launches replay from one CUDA graph
 
     def _local(self, hidden, topk_w, topk_ids, emap):
         if self._fn is not None:
@@ -395,6 +398,23 @@ class ExpertParallelMoEPrefill:
             w = self.weights
             self._alphas = nvfp4_moe_alphas(w[2], w[5], w[6], w[7])
         return nvfp4_moe_prefill(hidden, topk_w, topk_ids, *self.weights, expert_map=emap, alphas=self._alphas)
+
+    def _local_step(self, b, key):
+        """The local layer over the gathered buffers.  On CUDA ranks its launches (routing metadata, quantizer, two grouped
+        GEMMs, un-permute) are captured once per shape and replayed: with 1/G of the experts per rank the kernels are
+        short and a dozen separate Python-level launches would cost more than they run."""
+        if not self.use_graph or not b["h"].is_cuda:
+            return self._local(b["h"], b["w"], b["i"], self._emap)
+        g = self._graphs.get(key)
+        if g is None:
+            self._local(b["h"], b["w"], b["i"], self._emap)      # first run outside the capture: one-time initialisation
+            torch.cuda.synchronize(b["h"].device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self._local(b["h"], b["w"], b["i"], self._emap)
+            g = self._graphs[key] = (graph, out)
+        g[0].replay()
+        return g[1]
 
     def forward(self, hidden: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         if self._emap is None or self._emap.device != hidden.device:
@@ -406,13 +426,19 @@ class ExpertParallelMoEPrefill:
         k = topk_ids.shape[1]
         # routing travels as one [Tl, 2k] int32 block (ids | weight bits): two all-gathers instead of three
         route = torch.cat((topk_ids.to(torch.int32), topk_w.to(torch.float32).contiguous().view(torch.int32)), dim=1).contiguous()
-        h_all = torch.empty((G * Tl, H), dtype=hidden.dtype, device=hidden.device)
-        r_all = torch.empty((G * Tl, 2 * k), dtype=torch.int32, device=hidden.device)
-        dist.all_gather_into_tensor(h_all, hidden.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(r_all, route, group=self.group)
-        i_all = r_all[:, :k].contiguous()
-        w_all = r_all[:, k:].contiguous().view(torch.float32)
-        part = self._local(h_all, w_all, i_all, self._emap)          # [G*Tl, H] partial rows in the activation dtype
+        key = (Tl, H, k, hidden.dtype, hidden.device)
+        b = self._bufs.get(key)
+        if b is None:          # gathered inputs live in buffers of their own: their addresses are what a captured graph reads
+            b = self._bufs[key] = {
+                "h": torch.empty((G * Tl, H), dtype=hidden.dtype, device=hidden.device),
+                "r": torch.empty((G * Tl, 2 * k), dtype=torch.int32, device=hidden.device),
+                "i": torch.empty((G * Tl, k), dtype=torch.int32, device=hidden.device),
+                "w": torch.empty((G * Tl, k), dtype=torch.float32, device=hidden.device)}
+        dist.all_gather_into_tensor(b["h"], hidden.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(b["r"], route, group=self.group)
+        b["i"].copy_(b["r"][:, :k])
+        b["w"].view(torch.int32).copy_(b["r"][:, k:])
+        part = self._local_step(b, key)                              # [G*Tl, H] partial rows in the activation dtype
         if dist.get_backend(self.group) == "gloo":
             part = part.float().contiguous()
             dist.all_reduce(part, group=self.group)

@@ -229,6 +229,34 @@ def test_moe_prefill_layer_small():
     assert cos > 0.999
 
 
+def test_ep_prefill_local_step_replays_from_a_graph():
+    """The expert-parallel prefill layer captures its local layer (routing metadata, quantizer, grouped GEMMs, un-permute)
+    into a CUDA graph per shape; replays over new contents of the gathered buffers equal the eager calls."""
+    from dgx_vllm_b200 import grouped_moe as gm
+    from dgx_vllm_b200.moe_ep import ExpertParallelMoEPrefill, expert_map_for_rank
+    M, E, topk, H, I = 96, 8, 2, 256, 128
+    w13c, w13s, w13g = _expert_weights(E, 2 * I, H, 31)
+    w2c, w2s, w2g = _expert_weights(E, H, I, 32)
+    c = lambda a: torch.from_numpy(a).cuda()
+    a1 = np.full(E, 448.0 * 6.0 / 4.0, np.float32)
+    a2 = np.full(E, 448.0 * 6.0 / 1.0, np.float32)
+    weights = (c(w13c), c(_swizzle_experts(w13s)), c(w13g), c(w2c), c(_swizzle_experts(w2s)), c(w2g), c(a1), c(a2))
+    layer = ExpertParallelMoEPrefill(E, weights)
+    layer._emap = expert_map_for_rank(E, 1, 0, torch.device("cuda"))
+    bufs = {"h": torch.empty(M, H, dtype=torch.bfloat16, device="cuda"), "i": torch.empty(M, topk, dtype=torch.int32, device="cuda"),
+            "w": torch.empty(M, topk, dtype=torch.float32, device="cuda")}
+    for seed in (41, 42, 43):
+        tw, ids = _routing(M, E, topk, seed)
+        hidden = torch.randn(M, H, generator=torch.Generator().manual_seed(seed)).bfloat16()
+        bufs["h"].copy_(hidden)
+        bufs["i"].copy_(ids)
+        bufs["w"].copy_(tw)
+        out = layer._local_step(bufs, "k").clone()
+        ref = gm.nvfp4_moe_prefill(hidden.cuda(), tw.cuda(), ids.cuda(), *weights, expert_map=layer._emap)
+        assert torch.equal(out, ref)
+    assert "k" in layer._graphs
+
+
 def test_gather_quant_matches_shuffle_then_quant():
     from dgx_vllm_b200 import grouped_moe as gm
     T, H, E, topk = 37, 256, 6, 3
