@@ -93,12 +93,21 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may become resident while the kernel before it
+// on the stream drains; it must not touch that kernel's data before pdl_wait() returns (the earlier grid has then
+// completed and its writes are visible).  pdl_launch_dependents() lets the NEXT kernel do the same with this one.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Block 0 builds the plan; the remaining blocks (if any) copy / convert the activation matrix to fp16.
 __global__ void __launch_bounds__(kPlanThreads)
     moe_plan_kernel(const int32_t* __restrict__ ids, int P, const int32_t* __restrict__ expert_map, int global_E, int E,
                     Plan plan, const void* __restrict__ conv_src_v, __half* __restrict__ conv_dst,
                     int64_t conv_chunks, int ids_topk, int64_t ids_ld, int64_t conv_row_chunks, int64_t conv_ld_chunks,
                     int* zero_buf, int zero_count, int max_tok, int conv_mode) {
+  pdl_wait();                 // the kernel before this one may still be reading the workspace this one rewrites
+  pdl_launch_dependents();
   if (blockIdx.x > 0) {
     const uint4* conv_src = reinterpret_cast<const uint4*>(conv_src_v);
     const int64_t stride = (int64_t)(gridDim.x - 1) * kPlanThreads;
@@ -978,8 +987,6 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
 // Programmatic dependent launch: the GEMV and reduce kernels of a layer are launched with the stream-serialization
 // attribute, so their blocks may become resident while the kernel before them drains; pdl_wait() returns once that
 // kernel has completed and its writes are visible (at once when the launch carried no such attribute).
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -1433,6 +1440,7 @@ __global__ void weighted_reduce_kernel(const float* __restrict__ down, const flo
                                        const int* __restrict__ mapped, void* out, int out_dtype, int M, int topk, int H,
                                        int unweighted, int64_t ld_w, OutScatter sc) {
   pdl_wait();
+  pdl_launch_dependents();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   int m = blockIdx.y;
   if (sc.status_out != nullptr && h == 0 && m == 0) *sc.status_out = *sc.status_src;
@@ -1738,9 +1746,9 @@ void launch_plan(const int32_t* ids, int64_t P, int64_t ids_topk, int64_t ids_ld
     if (nb > 2 * (int64_t)sm_count()) nb = 2 * (int64_t)sm_count();
     blocks += (unsigned)(nb < 1 ? 1 : nb);
   }
-  moe_plan_kernel<<<blocks, kPlanThreads, 0, st>>>(ids, (int)P, expert_map, (int)global_E, (int)E, plan, a_src, a_f16, chunks,
-                                                   (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : 1, a_ld / 8, zero_buf,
-                                                   zero_count, max_tok, conv_mode);
+  launch_pdl(moe_plan_kernel, dim3(blocks), dim3(kPlanThreads), 0, st, ids, (int)P, expert_map, (int)global_E, (int)E, plan,
+             a_src, a_f16, chunks, (int)ids_topk, ids_ld, a_cols / 8 > 0 ? a_cols / 8 : (int64_t)1, a_ld / 8, zero_buf, zero_count,
+             max_tok, conv_mode);
 }
 
 // Runs one projection for P pairs with a plan already in `plan`.  A is fp16.
