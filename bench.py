@@ -682,6 +682,60 @@ def verify_layer_step(layer, batch0, w13, w2, world, rank, dev, n_tok: int = 4):
             "against": "CPU oracle (fp32 dequantize-then-matmul per routed expert), max|diff|/max|ref|"}
 
 
+def bench_ep_local_call(dev, flush, hbm_peak, ranks: int = 8, batch: int = 32, steps: int = 20):
+    """What ONE rank of an expert-parallel group of `ranks` GPUs runs per step, on this GPU alone: the fused layer over
+    the ranks*batch tokens of all ranks with only E_TOTAL/ranks experts resident (`expert_map` masks the others).  No
+    exchange: this isolates the local layer, whose GEMV launch has few items per SM and takes the 8-warp x 8-stage
+    shape of the warp-scheduled kernel.  Cold L2, CUDA events from the library's benchmark hook."""
+    import torch
+    import synth
+    from dgx_vllm_b200 import _lib, scaled_fp4_quant, sparse_fp4_v7 as sp7
+    from dgx_vllm_b200.moe_ep import expert_map_for_rank
+
+    def qfn(w, gs):
+        c, s_ = scaled_fp4_quant(w, gs, is_sf_swizzled_layout=False)
+        return c, s_.view(torch.uint8)
+
+    e_local = E_TOTAL // ranks
+    w13 = synth.make_sparse_experts(e_local, 2 * INTER, HIDDEN, 4000, dev, qfn)
+    w2 = synth.make_sparse_experts(e_local, HIDDEN, INTER, 5000, dev, qfn)
+    k4 = ("comp_T", "meta_T", "scale_T", "g_scales")
+    emap = expert_map_for_rank(E_TOTAL, ranks, 0, dev)
+    layer = sp7.FusedSparseMoE(*[w13[x] for x in k4], *[w2[x] for x in k4], INTER, expert_map=emap)
+    T = ranks * batch
+    cases = []
+    for i in range(N_ROUTINGS):
+        tw, ids = synth.make_routing(T, E_TOTAL, TOPK, 700 + i, dev)
+        cases.append((synth.make_hidden(T, HIDDEN, 800 + i, dev), tw, ids))
+    L = _lib.lib()
+    for i in range(3):
+        layer(*cases[i % N_ROUTINGS])
+    torch.cuda.synchronize()
+    t_layer, t_gemv, byts = [], [], []
+    for i in range(steps):
+        h, tw, ids = cases[i % N_ROUTINGS]
+        m = emap[ids.long()]
+        uniq, pairs = int(m[m >= 0].unique().numel()), int((m >= 0).sum().item())
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for e in ev:
+            e.record()
+        L.b200fp4_fused_moe_profile_events(ev[0].cuda_event, ev[1].cuda_event, ev[2].cuda_event)
+        a.record()
+        layer(h, tw, ids)
+        b.record()
+        L.b200fp4_fused_moe_profile_events(0, 0, 0)
+        torch.cuda.synchronize()
+        t_layer.append(a.elapsed_time(b) * 1e-3)
+        t_gemv.append(ev[0].elapsed_time(ev[2]) * 1e-3)
+        byts.append(uniq * (BYTES_PER_EXPERT_GATE_UP + BYTES_PER_EXPERT_DOWN) + pairs * (HIDDEN * 2 + INTER * 4 + HIDDEN * 4))
+    gbps = sum(byts) / sum(t_gemv) / 1e9
+    return {"layer_us": statistics.mean(t_layer) * 1e6, "gemv_launch_us": statistics.mean(t_gemv) * 1e6,
+            "gemv_GBps": gbps, "frac_of_measured_hbm": gbps / hbm_peak,
+            "config": f"{T} tokens ({ranks} ranks x {batch}), {e_local} local of {E_TOTAL} experts, top-{TOPK}, cold L2"}
+
+
 def bench_reference_v7_gpu(dev, w13, w2, batches, flush, ours, steps: int = 20):
     """The reference's own CUDA extension (sparse_fp4_kernel/sparse_fp4_v7.cu compiled unmodified for sm_100 by
     oracle/build_ref_v7.py) on the same tensors, inside its contract (identity expert_map, N >= 512; its lazy table
@@ -755,6 +809,9 @@ def main():
                     help="run just the dense GEMM / quantizer parts and print their numbers; a short command for "
                          "profiling those kernels (with --no-library-comparison the serving stack's kernel is not timed)")
     ap.add_argument("--no-library-comparison", action="store_true")
+    ap.add_argument("--only-ep-local", action="store_true",
+                    help="run just the `ep8_local_call` part (the layer one of eight expert-parallel ranks runs per step, "
+                         "on this GPU alone); a short command for profiling that launch shape")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -765,6 +822,13 @@ def main():
         torch.cuda.set_device(dev)
         hbm_peak, _ = measured_peaks()
         print(json.dumps(bench_dense_parts(dev, L2Flush(dev), hbm_peak, library=not args.no_library_comparison)))
+        return 0
+    if args.only_ep_local:
+        import torch
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        hbm_peak, _ = measured_peaks()
+        print(json.dumps({"ep8_local_call": bench_ep_local_call(dev, L2Flush(dev), hbm_peak)}))
         return 0
     if args.only_prefill:
         import torch
@@ -1004,6 +1068,7 @@ def main():
             del w13, w2, layer
             torch.cuda.empty_cache()
             line["parts"] = bench_dense_parts(dev, flush, hbm_peak)
+            line["parts"]["ep8_local_call"] = bench_ep_local_call(dev, flush, hbm_peak)
             line["parts"]["reference_v7_gpu"] = ref_gpu
             torch.cuda.empty_cache()
             line["parts"]["moe_prefill_8192_tokens"] = bench_moe_prefill(dev, flush, hbm_peak)

@@ -1049,9 +1049,8 @@ __global__ void __launch_bounds__(kMmaThreads, 1)
 // Epilogue from registers: the lane that holds 16 consecutive columns of a token writes them with 16-byte stores;
 // with SiLU the warp's 128 columns are 64 gate + the matching 64 up columns, the two halves of the warp swap one
 // token's values through shuffles, and SiLU(gate)*up leaves in fragment order for the down projection.
-// Two shapes of the same ring budget: 16 warps x 4 stages per block (the default), or 8 warps x 8 stages for launches with
-// few items (expert parallelism: a rank that owns 64 experts has about 550 gate_up items for 2368 warps; what bounds such
-// a launch is how many bytes ONE warp keeps in flight, so the idle warps' ring space goes to the busy ones).
+// Two shapes of the same ring budget: 8 warps x 8 stages per block (the default where K is a multiple of 256: two warps
+// per scheduler, each with twice the bytes in flight, measured faster at every batch size tried), or 16 warps x 4 stages.
 constexpr int kWsStages = 4;
 constexpr int kWsWarps = 16;
 constexpr int kWsThreads = 32 * kWsWarps;
@@ -1344,23 +1343,23 @@ __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const i
   return carry;
 }
 
-template <bool kSilu, int kN>
-__global__ void __launch_bounds__(kWsThreads, 1) sparse_gemv_ws_kernel(const GemvArgs g, int* counter) {
+template <bool kSilu, int kN, int kS = kWsStages, int kW = kWsWarps>
+__global__ void __launch_bounds__(32 * kW, 1) sparse_gemv_ws_kernel(const GemvArgs g, int* counter) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch_dependents();
-  const WsLane L = ws_lane(smem);
+  const WsLane L = ws_lane<kS>(smem);
   int first = 0;
   if (L.lane == 0) first = atomicAdd(counter, 1);
   first = __shfl_sync(0xffffffffu, first, 0);
-  ws_phase<kSilu, kN, 0>(g, counter, 0, first, L, nullptr, 0);
+  ws_phase<kSilu, kN, 0, kS>(g, counter, 0, first, L, nullptr, 0);
 }
 
 // Both projections of the MoE layer in one launch: the claim sequence runs through the gate_up items and on into the
 // down items, so a warp that finds no gate_up item left starts on the down projection of passes that are complete
 // instead of idling until the slowest warp of a first launch has finished and a second launch has ramped up.
-template <int kNA, int kNB, int kS = kWsStages>
-__global__ void __launch_bounds__(32 * (kWsStages * kWsWarps / kS), 1)
+template <int kNA, int kNB, int kS = kWsStages, int kW = kWsWarps>
+__global__ void __launch_bounds__(32 * kW, 1)
     fused_moe_ws_kernel(const GemvArgs ga, const GemvArgs gb, int* counter, int* done, int need) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
@@ -1639,12 +1638,12 @@ bool ws_ok(int64_t N, int64_t K, int64_t G, int64_t inter_silu, const SparseWeig
 // Opt a kernel in to the large dynamic shared memory, once per device; `attr_set` belongs to the caller, one array per
 // kernel instantiation (instantiations share their function type, so a static in here would be shared between them).
 template <typename Kernel>
-bool ws_prepare(Kernel kernel, bool* attr_set) {
+bool ws_prepare(Kernel kernel, bool* attr_set, size_t smem_bytes = kWsSmemBytes) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return false;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWsSmemBytes) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) != cudaSuccess) {
       cudaGetLastError();
       return false;
     }
@@ -1659,12 +1658,15 @@ int64_t ws_grid(int64_t max_items) {
   return grid < 1 ? 1 : grid;
 }
 
-template <bool kSilu, int kN>
+template <bool kSilu, int kN, int kS = kWsStages, int kW = kWsWarps>
 int launch_ws_t(const GemvArgs& g, int* counter, int64_t max_items, cudaStream_t st) {
   static bool attr_set[64] = {false};
-  if (!ws_prepare(sparse_gemv_ws_kernel<kSilu, kN>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
-  launch_pdl(sparse_gemv_ws_kernel<kSilu, kN>, dim3((unsigned)ws_grid(max_items)), dim3(kWsThreads), kWsSmemBytes, st, g,
-             counter);
+  constexpr size_t smem = (size_t)kW * kS * kWsStageBytes + 128;
+  if (!ws_prepare(sparse_gemv_ws_kernel<kSilu, kN, kS, kW>, attr_set, smem)) return B200FP4_STATUS_EXECUTION_FAILED;
+  int64_t grid = (max_items + kW - 1) / kW;
+  if (grid > (int64_t)sm_count()) grid = sm_count();
+  if (grid < 1) grid = 1;
+  launch_pdl(sparse_gemv_ws_kernel<kSilu, kN, kS, kW>, dim3((unsigned)grid), dim3(32 * kW), smem, st, g, counter);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -1678,21 +1680,26 @@ int run_projection_ws(const SparseWeights& w, const Plan& plan, const __half* A,
   GemvArgs g = make_args(w, plan, A, lda, a_div, out, out_dtype, ldo, N, K, inter_silu);
   g.n_slabs = inter_silu > 0 ? inter_silu / 64 : (int)(N / 128);
   const int64_t items = max_passes(P, E) * g.n_slabs;
+  if (K % 256 == 0) {      // 8 warps x 8-stage rings (see the fused layer for the measurements)
+    if (inter_silu > 0)
+      return N == 1024 ? launch_ws_t<true, 1024, 8, 8>(g, counter, items, st) : launch_ws_t<true, 0, 8, 8>(g, counter, items, st);
+    return N == 2048 ? launch_ws_t<false, 2048, 8, 8>(g, counter, items, st) : launch_ws_t<false, 0, 8, 8>(g, counter, items, st);
+  }
   if (inter_silu > 0) return N == 1024 ? launch_ws_t<true, 1024>(g, counter, items, st) : launch_ws_t<true, 0>(g, counter, items, st);
   return N == 2048 ? launch_ws_t<false, 2048>(g, counter, items, st) : launch_ws_t<false, 0>(g, counter, items, st);
 }
 
-template <int kNA, int kNB, int kS = kWsStages>
+template <int kNA, int kNB, int kS = kWsStages, int kW = kWsWarps>
 int launch_fused_ws_t(const GemvArgs& ga, const GemvArgs& gb, int* counter, int* done, int need, int64_t max_items,
                       cudaStream_t st) {
   static bool attr_set[64] = {false};
-  constexpr int warps = kWsStages * kWsWarps / kS;
-  if (!ws_prepare(fused_moe_ws_kernel<kNA, kNB, kS>, attr_set)) return B200FP4_STATUS_EXECUTION_FAILED;
-  int64_t grid = (max_items + warps - 1) / warps;
+  constexpr size_t smem = (size_t)kW * kS * kWsStageBytes + 128;
+  static_assert(smem <= 227 * 1024, "shared memory of the ring");
+  if (!ws_prepare(fused_moe_ws_kernel<kNA, kNB, kS, kW>, attr_set, smem)) return B200FP4_STATUS_EXECUTION_FAILED;
+  int64_t grid = (max_items + kW - 1) / kW;
   if (grid > (int64_t)sm_count()) grid = sm_count();
   if (grid < 1) grid = 1;
-  launch_pdl(fused_moe_ws_kernel<kNA, kNB, kS>, dim3((unsigned)grid), dim3(32 * warps), kWsSmemBytes, st, ga, gb, counter, done,
-             need);
+  launch_pdl(fused_moe_ws_kernel<kNA, kNB, kS, kW>, dim3((unsigned)grid), dim3(32 * kW), smem, st, ga, gb, counter, done, need);
   return B200FP4_STATUS_SUCCESS;
 }
 
@@ -2101,18 +2108,17 @@ static int fused_moe_impl(const void* hidden, int64_t ld_h, int h_dtype, const f
       gb.n_slabs = (int)(H / 128);
       const int need = ga.n_slabs + g_wait_extra_need;
       const int64_t items = max_passes(P, E) * (ga.n_slabs + gb.n_slabs);
-      // Few items (a rank of an expert-parallel group owns few experts): eight warps with eight-stage rings per block.
-      // The host only knows bounds: local pairs ~ P * E / global_E, passes of the first projection ~ min(E, local pairs).
-      const int64_t local_pairs = (expert_map && global_E > 0) ? P * E / global_E : P;
-      const int64_t est_items_a = (local_pairs < E ? local_pairs : E) * ga.n_slabs;
-      // (measured at 8 ranks x 32 tokens, 64 local experts: the GEMV launch takes 49.7 us with 16 warps x 4 stages,
-      // 37.6 us with 8 x 8, 44.7 us with 4 x 16)
-      const bool deep = est_items_a <= (int64_t)sm_count() * 8 && H % 256 == 0 && I % 256 == 0;
+      // Block shape: 8 warps with 8-stage rings where K allows (both K multiples of 256), else 16 warps x 4 stages.
+      // Measured on B200 (layer step / fraction of the copy bandwidth of the launch, batch 32, 512 experts):
+      // 8 x 8: 72.4 us / 0.745; 7 x 8: 73.5 / 0.73; 8 warps x 4 stages: 73.7 / 0.72; 16 x 4: 76.0 / 0.705; 6 x 8: 78.2; 12 x 4:
+      // 79.6; 9, 10, 12 warps x 8: 79-82; 6 or 5 warps x 16 stages: 78.5 / 82.5; 4 x 8: 87.4; 24 x 4: 93.7.  With the 64
+      // local experts of one of eight expert-parallel ranks: 16 x 4 49.7 us for the launch, 8 x 8 37.6 us, 4 x 16 44.7 us.
+      const bool deep = H % 256 == 0 && I % 256 == 0;
       if (2 * I == 1024 && H == 2048) {
-        rc = deep ? launch_fused_ws_t<1024, 2048, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
+        rc = deep ? launch_fused_ws_t<1024, 2048, 8, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
                   : launch_fused_ws_t<1024, 2048>(ga, gb, plan.hdr + 2, done, need, items, st);
       } else {
-        rc = deep ? launch_fused_ws_t<0, 0, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
+        rc = deep ? launch_fused_ws_t<0, 0, 8, 8>(ga, gb, plan.hdr + 2, done, need, items, st)
                   : launch_fused_ws_t<0, 0>(ga, gb, plan.hdr + 2, done, need, items, st);
       }
       if (rc != B200FP4_STATUS_SUCCESS) return rc;
