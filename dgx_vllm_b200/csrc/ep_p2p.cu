@@ -50,6 +50,10 @@ __global__ void __launch_bounds__(256)
     ep_dispatch_p2p_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ ids, const float* __restrict__ w, int B,
                            int H, int topk, int G, int rank, int64_t rec_chunks, uint4* const* __restrict__ rec_ptrs,
                            int* const* __restrict__ flag_ptrs, int seq, int* scratch, long long budget) {
+  // launched with the programmatic attribute: resident early, but nothing is read or stored before the kernels ahead on
+  // the stream (the producer of the activations, this rank's combine of the previous step) have completed
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   const int h_chunks = H / 8;
   __shared__ uint4 s_tail[64];
@@ -86,6 +90,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
     ep_combine_p2p_kernel(const float* __restrict__ parts, int B, int H, int G, int rank, int* const* __restrict__ flag_ptrs,
                           int seq, int* scratch, long long budget, T* __restrict__ out) {
+  pdl_wait();          // the kernel before this one on the stream stored this rank's partial rows into the peers' buffers
+  pdl_launch_dependents();
   if ((int)threadIdx.x < G) {
     // the kernel before this one on the stream stored this rank's partial rows into the peers' buffers
     if (blockIdx.x == 0) {
@@ -124,9 +130,10 @@ extern "C" int b200fp4_ep_dispatch_p2p(const void* hidden, const int32_t* topk_i
   if (!hidden || !topk_ids || !topk_weights || !record_ptrs || !flag_ptrs || !scratch || !aligned(hidden, 16))
     return B200FP4_STATUS_INVALID_VALUE;
   const int64_t rec_chunks = (int64_t)b200fp4_ep_record_bytes(H, topk) / 16;
-  ep_dispatch_p2p_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(
-      reinterpret_cast<const uint4*>(hidden), topk_ids, topk_weights, (int)B, (int)H, (int)topk, (int)G, (int)rank, rec_chunks,
-      reinterpret_cast<uint4* const*>(record_ptrs), reinterpret_cast<int* const*>(flag_ptrs), seq, scratch, kEpWaitCycles);
+  launch_pdl(ep_dispatch_p2p_kernel, dim3((unsigned)B), dim3(256), 0, (cudaStream_t)stream,
+             reinterpret_cast<const uint4*>(hidden), topk_ids, topk_weights, (int)B, (int)H, (int)topk, (int)G, (int)rank, rec_chunks,
+             reinterpret_cast<uint4* const*>(record_ptrs), reinterpret_cast<int* const*>(flag_ptrs), (int)seq, scratch,
+             kEpWaitCycles);
   return finish_launch(1);
 }
 
@@ -139,12 +146,12 @@ extern "C" int b200fp4_ep_combine_p2p(const float* parts, int64_t B, int64_t H, 
   int64_t blocks = (B * H / 4 + 255) / 256;
   if (blocks > 2 * (int64_t)sm_count()) blocks = 2 * (int64_t)sm_count();
   if (out_dtype == B200FP4_DTYPE_BF16)
-    ep_combine_p2p_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        parts, (int)B, (int)H, (int)G, (int)rank, reinterpret_cast<int* const*>(flag_ptrs), seq, scratch, kEpWaitCycles,
-        reinterpret_cast<__nv_bfloat16*>(out));
+    launch_pdl(ep_combine_p2p_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, parts, (int)B,
+               (int)H, (int)G, (int)rank, reinterpret_cast<int* const*>(flag_ptrs), (int)seq, scratch, kEpWaitCycles,
+               reinterpret_cast<__nv_bfloat16*>(out));
   else
-    ep_combine_p2p_kernel<__half><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        parts, (int)B, (int)H, (int)G, (int)rank, reinterpret_cast<int* const*>(flag_ptrs), seq, scratch, kEpWaitCycles,
-        reinterpret_cast<__half*>(out));
+    launch_pdl(ep_combine_p2p_kernel<__half>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, parts, (int)B, (int)H,
+               (int)G, (int)rank, reinterpret_cast<int* const*>(flag_ptrs), (int)seq, scratch, kEpWaitCycles,
+               reinterpret_cast<__half*>(out));
   return finish_launch(1);
 }

@@ -93,12 +93,6 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t w) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Programmatic dependent launch: a kernel launched with the attribute may become resident while the kernel before it
-// on the stream drains; it must not touch that kernel's data before pdl_wait() returns (the earlier grid has then
-// completed and its writes are visible).  pdl_launch_dependents() lets the NEXT kernel do the same with this one.
-// Without the launch attribute both are no-ops.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Block 0 builds the plan; the remaining blocks (if any) copy / convert the activation matrix to fp16.
 __global__ void __launch_bounds__(kPlanThreads)
@@ -988,23 +982,6 @@ __device__ __forceinline__ void gemv_mma_phase(const GemvArgs& g, unsigned char*
 // attribute, so their blocks may become resident while the kernel before them drains; pdl_wait() returns once that
 // kernel has completed and its writes are visible (at once when the launch carried no such attribute).
 
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  // not while a CUDA graph is being captured: replayed graphs have no launch gap to hide, and the 48-layer decode stack
-  // measured 3-4 % slower with programmatic edges than with plain ones
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  cfg.numAttrs = (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
 
 template <int CG, int S, bool kSilu, int TM>
 __global__ void __launch_bounds__(kMmaThreads, 1) sparse_gemv_mma_kernel(const GemvArgs g) {
