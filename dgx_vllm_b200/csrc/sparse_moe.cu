@@ -1084,9 +1084,12 @@ __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const i
   const int n_items = g.plan.hdr[1] * groups;
   if (first - base >= n_items) return first;
 
+  // warp w of the grid starts on item w without asking (one round trip to the counter less before the first byte is
+  // requested); the counter hands out the items after those
+  const int n_warps = (int)(gridDim.x * (blockDim.x >> 5));
   auto claim = [&]() {
     int v = 0;
-    if (lane == 0) v = atomicAdd(counter, 1);
+    if (lane == 0) v = atomicAdd(counter, 1) + n_warps;
     return __shfl_sync(0xffffffffu, v, 0);
   };
   // An item as read from its pass record: expert, group, and the pairs this lane deals with (B column q; the one or two
@@ -1326,9 +1329,7 @@ __global__ void __launch_bounds__(32 * kW, 1) sparse_gemv_ws_kernel(const GemvAr
   pdl_wait();
   pdl_launch_dependents();
   const WsLane L = ws_lane<kS>(smem);
-  int first = 0;
-  if (L.lane == 0) first = atomicAdd(counter, 1);
-  first = __shfl_sync(0xffffffffu, first, 0);
+  int first = (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
   ws_phase<kSilu, kN, 0, kS>(g, counter, 0, first, L, nullptr, 0);
 }
 
@@ -1342,9 +1343,7 @@ __global__ void __launch_bounds__(32 * kW, 1)
   pdl_wait();
   pdl_launch_dependents();
   const WsLane L = ws_lane<kS>(smem);
-  int first = 0;
-  if (L.lane == 0) first = atomicAdd(counter, 1);
-  first = __shfl_sync(0xffffffffu, first, 0);
+  int first = (int)(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
   const int n_a = ga.plan.hdr[1] * ga.n_slabs;
   first = ws_phase<true, kNA, 1, kS>(ga, counter, 0, first, L, done, need);
   ws_phase<false, kNB, 2, kS>(gb, counter, n_a, first, L, done, need);
