@@ -39,7 +39,7 @@ BYTES_PER_EXPERT_DOWN = HIDDEN * INTER * 7 // 16
 N_ROUTINGS = 8
 # dram__bytes_read.sum + dram__bytes_write.sum of the gate_up and down GEMV launches of one layer, per routed expert,
 # from the ncu capture whose summary is committed with the profiles (244 routed experts: 233.61 MB + 118.83 MB)
-NCU_TRAFFIC_BYTES_PER_EXPERT = (323.85e6 + 5.18e6) / 244.0
+NCU_TRAFFIC_BYTES_PER_EXPERT = (323.90e6 + 4.31e6) / 244.0
 NCU_TRAFFIC_SOURCE = "ncu capture of the one-launch GEMV kernel (batch 32, 244 routed experts), scaled by routed experts"
 
 
