@@ -1072,8 +1072,10 @@ __device__ __forceinline__ WsLane ws_lane(unsigned char* smem) {
 // kDep links the two projections of the MoE layer when they run in one launch: 1 = producer (done[pass] counts the
 // finished items of a pass, fenced), 2 = consumer (the B fragments of an item -- the activations the producer wrote
 // for that pass -- are fetched only once done[pass] has reached `need`), 0 = stand-alone.
-// A consumer only ever waits for items that running warps hold (an item of the first projection is claimed before any
-// item of the second), so the wait cannot deadlock; it is bounded all the same and reports through the status word.
+// A consumer only ever waits for items of the first projection, and each of those is held either by a running warp (it
+// was claimed before any item of the second projection) or by the warp of this grid it is statically assigned to (index <
+// number of warps; the grid has at most one block per SM, so that warp becomes resident without anyone's help): the wait
+// cannot deadlock; it is bounded all the same and reports through the status word.
 template <bool kSilu, int kN, int kDep, int kS = kWsStages>
 __device__ __forceinline__ int ws_phase(const GemvArgs& g, int* counter, const int base, int first, const WsLane& L,
                                         int* done, const int need) {
