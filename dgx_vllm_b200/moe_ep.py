@@ -360,7 +360,8 @@ class ExpertParallelMoE:
         if self.world == 1 and self._fn is None:
             self._bound_layer(device).wait_host()
             return
-        torch.cuda.current_stream(device).synchronize()
+        if self._fn is None:         # CPU ranks have nothing queued
+            torch.cuda.current_stream(device).synchronize()
 
 
 class ExpertParallelMoEPrefill:

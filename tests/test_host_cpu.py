@@ -118,6 +118,12 @@ for mode in ("gather", "a2a"):      # all-gather + reduce-scatter of fp32 partia
     out = layer.forward(hidden, tw, ids)
     err = float(np.max(np.abs(out.float().numpy() - ref)) / np.max(np.abs(ref)))
     assert err < 2e-2, (mode, err)          # the stand-in returns 16-bit partial rows per owner rank
+    # the host-buffer entry points on CPU ranks: nothing to queue, the result is there on return
+    out_host = torch.empty_like(hidden)
+    assert layer.submit_host(hidden, tw, ids, out_host, torch.device("cpu")) is None
+    layer.wait_host(torch.device("cpu"))
+    assert torch.equal(out_host, out)
+    assert torch.equal(layer.forward_host(hidden, tw, ids, torch.empty_like(hidden), torch.device("cpu")), out)
 print(f"rank {rank} ok err={err:.3e}")
 dist.destroy_process_group()
 '''
