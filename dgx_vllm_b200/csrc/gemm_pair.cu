@@ -6,9 +6,10 @@
 // the pair issues every 176 cycles; M=4096, N=14336, K=4096 takes about 200 k cycles against 223 k for the single-CTA
 // kernel (123 us against 129 us: the SM clock settles near 1.6-1.7 GHz under either).
 //
-// Roles per CTA (15 warps): warp 0 loads operands, warp 1 issues the MMAs (leader CTA only) and owns tensor memory,
-// warps 2-5 and 10-13 drain and store the CTA's 128 accumulator rows, warps 6-9 move scale factors from shared memory
-// into tensor memory, warp 14 loads scale factors.
+// Roles per CTA (23 warps): warp 0 loads operands, warp 1 issues the MMAs (leader CTA only) and owns tensor memory,
+// warps 2-5, 10-13 and 15-22 drain and store the CTA's 128 accumulator rows (four warps per tensor-memory lane quarter, 64
+// columns each: the one accumulator is handed back after two tcgen05.ld per warp), warps 6-9 move scale factors from
+// shared memory into tensor memory, warp 14 loads scale factors.
 //
 // What keeps the stage loop short (a stage = 256 k = 4 MMAs = about 700 cycles, less than the latency of a load, so
 // every hop between "stage free" and "stage ready" counts):
@@ -29,7 +30,7 @@
 namespace b200fp4 {
 namespace {
 
-constexpr int kPairThreads = 480;
+constexpr int kPairThreads = 736;
 constexpr int kPStages = 5;                        // operand ring
 constexpr int kPSfStages = 10;                     // scale-factor ring (shared memory)
 constexpr int kPStageA = 128 * 128;                // 128 rows x 128 bytes (256 k)
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       mbar_init(smem_u32(&sf_free[j]), 4);        // one arrival per scale warp
     }
     mbar_init(smem_u32(acc_full), 1);
-    mbar_init(smem_u32(acc_empty), 16);           // one arrival per epilogue warp of both CTAs
+    mbar_init(smem_u32(acc_empty), 32);           // one arrival per epilogue warp of both CTAs
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -268,10 +269,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (both CTAs, warps 2..5 and 10..13)
-    // Two warps per tensor-memory lane quarter, each draining and storing 128 of the tile's 256 columns.
+    // ------------------------------------------------------------------ epilogue (both CTAs, warps 2..5, 10..13, 15..22)
+    // Four warps per tensor-memory lane quarter, each draining and storing 64 of the tile's 256 columns (with two warps per
+    // quarter the MMA thread waited about 1200 cycles per tile for the drain; M=4096: 121 us against 123 us).
     const int quarter = warp & 3;
-    const int c_first = warp >= 10 ? 4 : 0;
+    const int grp = warp < 6 ? 0 : (warp < 14 ? 1 : (warp < 19 ? 2 : 3));     // warps 2-5, 10-13, 15-18, 19-22
+    const int c_first = grp * 2;
     const float alpha = p.alpha[0];
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(acc_empty), 0);
     uint32_t tcount = 0;
@@ -284,9 +287,9 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       tcgen05_fence_after();
       const int row = mp * 256 + (int)rank * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      uint32_t packed[64];
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tcgen05_ld_32x32(taddr + (c_first + c) * 32, r);
         tcgen05_wait_ld();
@@ -311,7 +314,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
       if (row < p.M) {
         uint16_t* dst_row = reinterpret_cast<uint16_t*>(p.out) + (size_t)row * p.N;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           const int col0 = nt * 256 + (c_first + c) * 32;
           if (col0 < p.N) {
             uint16_t* dst = dst_row + col0;
